@@ -42,11 +42,13 @@ PAGE_SIZE = 64  # tokens per page: BLOCK of lua/lgml/transformer.lua:30
 
 @dataclass(frozen=True)
 class PagedKV:
-    """Keys and values of every position (window None) or of the last ``window``."""
+    """Keys and values of every position (window None) or of the last ``window``.  Values
+    have the keys' head size unless ``v_head_dim`` gives their own."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -136,9 +138,10 @@ class CacheManager:
                 raise TypeError(f"layer {layer}: unknown cache spec {spec!r}")
         for grp in self.groups:
             shape = (grp.pool.n_pages, grp.spec.n_kv_heads, page_size, grp.spec.head_dim)
+            v_shape = shape[:3] + (grp.spec.v_head_dim or grp.spec.head_dim,)
             for layer in grp.layers:
                 grp.k[layer] = torch.zeros(shape, dtype=dtype, device=self.device)
-                grp.v[layer] = torch.zeros(shape, dtype=dtype, device=self.device)
+                grp.v[layer] = torch.zeros(v_shape, dtype=dtype, device=self.device)
         for sg in self.state_groups:
             for layer in sg.layers:
                 sg.state[layer] = torch.zeros((max_slots,) + tuple(sg.spec.shape), dtype=sg.spec.dtype, device=self.device)
@@ -165,7 +168,7 @@ class CacheManager:
     def bytes_held(self) -> int:
         n = 0
         for g in self.groups:
-            n += sum(t.numel() * t.element_size() for t in g.k.values()) * 2
+            n += sum(t.numel() * t.element_size() for t in g.k.values()) + sum(t.numel() * t.element_size() for t in g.v.values())
         for sg in self.state_groups:
             n += sum(t.numel() * t.element_size() for t in sg.state.values())
         return n

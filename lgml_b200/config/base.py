@@ -69,9 +69,13 @@ def lookup_architecture(name: str):
 
 
 def architecture_of(d: Dict[str, Any]) -> str:
+    """The name under ``architectures`` (a list, its first entry) or ``architecture`` (the name itself)."""
+    one = d.get("architecture")
+    if isinstance(one, str) and one and "architectures" not in d:
+        return one
     archs = d.get("architectures")
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: 'architectures' must be a list holding the architecture's name")
+        raise ConfigError("config.json: 'architectures' must be a list holding the architecture's name (or 'architecture' the name)")
     return archs[0]
 
 
@@ -93,6 +97,10 @@ def load_config(folder) -> ModelConfig:
     if not isinstance(d, dict):
         raise ConfigError(f"{path}: top level must be an object")
     cfg = config_from_dict(d)
+    # sizes that an architecture reads from the shapes of the folder's tensors
+    complete = getattr(cfg, "complete_from_folder", None)
+    if complete is not None:
+        complete(folder)
     # a folder's generation_config.json may name more end tokens than config.json (chat models end a
     # turn with another id than the text's end): a reply stops at any of them
     ids = generation_eos_ids(folder)

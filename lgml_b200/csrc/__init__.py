@@ -44,6 +44,8 @@ LIBRARIES: Dict[str, tuple] = {
     "attention_prefill_tc": ("attention_prefill_tc.cu", []),
     "attention_prefill_twin": ("attention_prefill_twin.cu", []),
     "attention_decode_noalloc": ("attention_decode_noalloc.cu", []),
+    "attention_sink": ("attention_sink.cu", []),
+    "delta_rule": ("delta_rule.cu", []),
 }
 
 _HEADERS = ["common.cuh", "page_map.cuh"]

@@ -1,0 +1,264 @@
+// The gated delta rule with a decay per key channel, and what surrounds it in a mixer: short
+// causal convolutions with SiLU on q, k and v, unit-length q and k, the write strength beta, the
+// decay, the recurrence itself, and the gated per-head RMS norm of what it reads out.
+//
+// Per head, with S [D, Dv] (float32, zero when a request starts), for each token in order:
+//     S <- g * S            (row d scaled by g_d = exp(-exp(A_log) * softplus(a_d + dt_bias_d)))
+//     u  = beta * (v - S^T k)
+//     S <- S + k u^T
+//     o  = S^T q            (the read-out sees this token's write)
+// Everything here is float32: the projections come in as float32, and the state of a request
+// (S of every head, then the last taps - 1 inputs of the convolutions) lives in one float32
+// vector per request slot.
+//
+// Four kernels a step:
+//   delta_prepare      one block per token, all tokens at once: convolution (the inputs before a
+//                      portion's first token come from the slot), SiLU, norms, beta, decay
+//   delta_conv_state   per request: the slot's last taps - 1 inputs after this step
+//   delta_scan         per (request, head, group of value columns): the recurrence over the
+//                      request's tokens in order.  A thread owns rows d = r, r + R, ... of one
+//                      column of S in registers; the R threads of a column add up S^T k and S^T q
+//                      by shuffles in a fixed order.  Columns never talk to each other, so the
+//                      result does not depend on how a prompt was cut or what else is in the batch.
+//   delta_output       per (token, head): o / rms(o) * weight * sigmoid(gate)
+#include <math.h>
+
+#include "common.cuh"
+
+LGML_DEFINE_LAST_ERROR(lgml_delta_rule)
+
+namespace {
+constexpr int PREP_THREADS = 256;
+constexpr int MAX_TAPS = 16;
+constexpr int SCAN_THREADS = 128;
+constexpr int TCH = 8;            // tokens whose k, q, decay, v and beta a block stages at a time
+
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// proj columns: q (G D) | k (G D) | v (H Dv) | beta (H) | ...   conv_w: [C, taps], C = 2 G D + H Dv, rows in that order.
+// out_c [tokens, C]: q (unit length, times D^-1/2) | k (unit length) | v, after convolution and SiLU.
+__global__ void __launch_bounds__(PREP_THREADS) delta_prepare_kernel(
+    const float *__restrict__ proj, int ldp, const float *__restrict__ a_pre, int lda, const float *__restrict__ conv_w, int taps,
+    const float *__restrict__ state, long long state_stride, long long conv_off, const int *__restrict__ seq_of_token,
+    const int *__restrict__ seq_start, const int *__restrict__ slots, const float *__restrict__ a_log,
+    const float *__restrict__ dt_bias, float *__restrict__ out_c, float *__restrict__ beta, float *__restrict__ decay, int H, int G,
+    int D, int Dv) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float buf[];             // the token's C channels after convolution and SiLU
+    const int t = blockIdx.x, tid = threadIdx.x;
+    const int C = 2 * G * D + H * Dv;
+    const int seq = seq_of_token[t];
+    const int i = t - seq_start[seq];          // index of the token in its request's portion
+    const float *old = state + (size_t)slots[seq] * state_stride + conv_off;   // [(taps - 1), C]: inputs at portion indices -(taps-1) .. -1
+    for (int c = tid; c < C; c += PREP_THREADS) {
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {       // input j tokens back, weighed by column taps - 1 - j
+            const int idx = i - j;
+            const float x = idx >= 0 ? act_load(proj + (size_t)(t - j) * ldp + c) : act_load(old + (size_t)(taps - 1 + idx) * C + c);
+            acc = fmaf(conv_w[(size_t)c * taps + (taps - 1 - j)], x, acc);
+        }
+        buf[c] = acc * sigmoid_f(acc);
+    }
+    __syncthreads();
+    const int lane = tid & 31, warp = tid >> 5;
+    float *dst = out_c + (size_t)t * C;
+    for (int hd = warp; hd < 2 * G; hd += PREP_THREADS / 32) {       // q heads, then k heads
+        float ss = 0.f;
+        for (int d = lane; d < D; d += 32) ss = fmaf(buf[hd * D + d], buf[hd * D + d], ss);
+        ss = warp_sum(ss);
+        float inv = 1.0f / sqrtf(ss + 1e-6f);
+        if (hd < G) inv *= 1.0f / sqrtf((float)D);
+        for (int d = lane; d < D; d += 32) dst[hd * D + d] = buf[hd * D + d] * inv;
+    }
+    for (int c = 2 * G * D + tid; c < C; c += PREP_THREADS) dst[c] = buf[c];
+    for (int h = tid; h < H; h += PREP_THREADS) beta[(size_t)t * H + h] = sigmoid_f(act_load(proj + (size_t)t * ldp + C + h));
+    for (int e = tid; e < H * D; e += PREP_THREADS) {
+        const float rate = expf(a_log[e / D]);
+        decay[(size_t)t * H * D + e] = expf(-rate * softplus_f(act_load(a_pre + (size_t)t * lda + e) + dt_bias[e]));
+    }
+}
+
+__global__ void __launch_bounds__(PREP_THREADS) delta_conv_state_kernel(
+    const float *__restrict__ proj, int ldp, int taps, float *__restrict__ state, long long state_stride, long long conv_off,
+    const int *__restrict__ seq_start, const int *__restrict__ slots, int C) {
+    pdl_trigger();
+    pdl_wait();
+    const int s = blockIdx.x, c = blockIdx.y * PREP_THREADS + threadIdx.x;
+    if (c >= C) return;
+    const int t0 = seq_start[s], n = seq_start[s + 1] - t0;
+    float *st = state + (size_t)slots[s] * state_stride + conv_off;
+    float old[MAX_TAPS];
+#pragma unroll
+    for (int r = 0; r < MAX_TAPS; ++r)
+        if (r < taps - 1) old[r] = st[(size_t)r * C + c];
+#pragma unroll
+    for (int r = 0; r < MAX_TAPS; ++r)
+        if (r < taps - 1) {
+            const int idx = n - (taps - 1) + r;     // the portion's index that row r holds after this step
+            st[(size_t)r * C + c] = idx >= 0 ? act_load(proj + (size_t)(t0 + idx) * ldp + c) : old[taps - 1 + idx];
+        }
+}
+
+// NPT rows of one column of S per thread; R threads (a power of two, neighbours in a warp) per column.
+template <int NPT>
+__global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
+    const float *__restrict__ qkv_c, const float *__restrict__ beta, const float *__restrict__ decay, float *__restrict__ state,
+    long long state_stride, const int *__restrict__ seq_start, const int *__restrict__ slots, float *__restrict__ o_out, int H, int G,
+    int D, int Dv, int R) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float sm[];
+    const int DP = NPT * R;                               // rows covered (>= D); rows past D hold k = q = 0, decay = 1
+    const int cols = SCAN_THREADS / R;
+    float *k_s = sm, *q_s = k_s + TCH * DP, *g_s = q_s + TCH * DP, *v_s = g_s + TCH * DP, *b_s = v_s + TCH * cols;
+    const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int g = h / (H / G);
+    const int r = tid % R, col_local = tid / R;
+    const int col = blockIdx.z * cols + col_local;
+    const bool active = col < Dv;
+    const int C = 2 * G * D + H * Dv;
+    const int t0 = seq_start[s], n = seq_start[s + 1] - t0;
+    float *S_base = state + (size_t)slots[s] * state_stride + (size_t)h * D * Dv;
+
+    float S[NPT];
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int d = r + R * i;
+        S[i] = (active && d < D) ? S_base[(size_t)d * Dv + col] : 0.f;
+    }
+    for (int c0 = 0; c0 < n; c0 += TCH) {
+        const int nt = min(TCH, n - c0);
+        __syncthreads();
+        for (int e = tid; e < nt * DP; e += SCAN_THREADS) {
+            const int i = e / DP, d = e - i * DP;
+            const size_t t = (size_t)(t0 + c0 + i);
+            const bool in = d < D;
+            q_s[e] = in ? act_load(qkv_c + t * C + g * D + d) : 0.f;
+            k_s[e] = in ? act_load(qkv_c + t * C + G * D + g * D + d) : 0.f;
+            g_s[e] = in ? act_load(decay + (t * H + h) * D + d) : 1.f;
+        }
+        for (int e = tid; e < nt * cols; e += SCAN_THREADS) {
+            const int i = e / cols, cl = e - i * cols;
+            const int cc = blockIdx.z * cols + cl;
+            v_s[e] = cc < Dv ? act_load(qkv_c + (size_t)(t0 + c0 + i) * C + 2 * G * D + h * Dv + cc) : 0.f;
+        }
+        for (int i = tid; i < nt; i += SCAN_THREADS) b_s[i] = act_load(beta + (size_t)(t0 + c0 + i) * H + h);
+        __syncthreads();
+        for (int i = 0; i < nt; ++i) {
+            const float *kk = k_s + i * DP + r, *qq = q_s + i * DP + r, *gg = g_s + i * DP + r;
+            float ks = 0.f;
+#pragma unroll
+            for (int j = 0; j < NPT; ++j) {
+                S[j] *= gg[R * j];
+                ks = fmaf(kk[R * j], S[j], ks);
+            }
+            for (int o = 1; o < R; o <<= 1) ks += __shfl_xor_sync(0xffffffffu, ks, o);
+            const float u = b_s[i] * (v_s[i * cols + col_local] - ks);
+            float oq = 0.f;
+#pragma unroll
+            for (int j = 0; j < NPT; ++j) {
+                S[j] = fmaf(kk[R * j], u, S[j]);
+                oq = fmaf(qq[R * j], S[j], oq);
+            }
+            for (int o = 1; o < R; o <<= 1) oq += __shfl_xor_sync(0xffffffffu, oq, o);
+            if (active && r == 0) o_out[(size_t)(t0 + c0 + i) * H * Dv + (size_t)h * Dv + col] = oq;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int d = r + R * i;
+        if (active && d < D) S_base[(size_t)d * Dv + col] = S[i];
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) delta_output_kernel(const float *__restrict__ o, const float *__restrict__ weight,
+                                                           const float *__restrict__ gate, int ldg, T *__restrict__ out, int ldo, int H,
+                                                           int Dv, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[32];
+    const int t = blockIdx.x, h = blockIdx.y;
+    const float *row = o + ((size_t)t * H + h) * Dv;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
+        const float v = act_load(row + d);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)Dv + eps);
+    for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
+        const float v = act_load(row + d) * inv * weight[d] * sigmoid_f(act_load(gate + (size_t)t * ldg + (size_t)h * Dv + d));
+        out[(size_t)t * ldo + (size_t)h * Dv + d] = from_f32<T>(v);
+    }
+}
+
+template <int NPT>
+int launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const float *qkv_c, const float *beta, const float *decay, float *state,
+                long long state_stride, const int *seq_start, const int *slots, float *o_out, int H, int G, int D, int Dv, int R) {
+    lgml_launch(delta_scan_kernel<NPT>, grid, SCAN_THREADS, smem, stream, qkv_c, beta, decay, state, state_stride, seq_start, slots, o_out, H,
+                G, D, Dv, R);
+    return lgml_launch_status("delta_scan");
+}
+}  // namespace
+
+LGML_API int lgml_delta_prepare(const float *proj, int ldp, const float *a_pre, int lda, const float *conv_w, int taps, float *state,
+                                long long state_stride, long long conv_off, const int *seq_of_token, const int *seq_start,
+                                const int *slots, const float *a_log, const float *dt_bias, float *out_c, float *beta, float *decay,
+                                int n_tokens, int n_seqs, int H, int G, int D, int Dv, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && n_seqs >= 0 && H > 0 && G > 0 && D > 0 && Dv > 0, "delta_prepare: bad sizes");
+    LGML_REQUIRE(H % G == 0, "delta_prepare: %d heads are no multiple of %d key heads", H, G);
+    LGML_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "delta_prepare: %d taps (1 to %d)", taps, MAX_TAPS);
+    const int C = 2 * G * D + H * Dv;
+    LGML_REQUIRE(ldp >= C + H && lda >= H * D, "delta_prepare: a row stride is below its columns");
+    LGML_REQUIRE((size_t)C * sizeof(float) <= 48 * 1024, "delta_prepare: %d channels are more than a block's shared memory holds", C);
+    if (n_tokens == 0) return 0;
+    lgml_launch(delta_prepare_kernel, dim3(n_tokens), PREP_THREADS, (size_t)C * sizeof(float), stream, proj, ldp, a_pre, lda, conv_w, taps,
+                (const float *)state, state_stride, conv_off, seq_of_token, seq_start, slots, a_log, dt_bias, out_c, beta, decay, H, G, D, Dv);
+    int rc = lgml_launch_status("delta_prepare");
+    if (rc || taps == 1) return rc;
+    lgml_launch(delta_conv_state_kernel, dim3(n_seqs, (C + PREP_THREADS - 1) / PREP_THREADS), PREP_THREADS, 0, stream, proj, ldp, taps, state,
+                state_stride, conv_off, seq_start, slots, C);
+    return lgml_launch_status("delta_conv_state");
+}
+
+LGML_API int lgml_delta_scan(const float *qkv_c, const float *beta, const float *decay, float *state, long long state_stride,
+                             const int *seq_start, const int *slots, float *o_out, int n_seqs, int H, int G, int D, int Dv,
+                             cudaStream_t stream) {
+    LGML_REQUIRE(n_seqs >= 0 && H > 0 && G > 0 && D > 0 && Dv > 0 && H % G == 0, "delta_scan: bad sizes");
+    LGML_REQUIRE(D <= 1024, "delta_scan: key size %d is over 1024", D);
+    LGML_REQUIRE(H <= 65535, "delta_scan: too many heads");
+    if (n_seqs == 0) return 0;
+    int R = 1;
+    while (R < 32 && (D + R - 1) / R > 32) R *= 2;       // at most 32 rows a thread
+    const int rows = (D + R - 1) / R;
+    const int npt = rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
+    const int cols = SCAN_THREADS / R;
+    const size_t smem = sizeof(float) * ((size_t)TCH * (3 * (size_t)npt * R + cols) + TCH);
+    dim3 grid(n_seqs, H, (Dv + cols - 1) / cols);
+#define LGML_SCAN_ARGS grid, smem, stream, qkv_c, beta, decay, state, state_stride, seq_start, slots, o_out, H, G, D, Dv, R
+    switch (npt) {
+        case 4: return launch_scan<4>(LGML_SCAN_ARGS);
+        case 8: return launch_scan<8>(LGML_SCAN_ARGS);
+        case 16: return launch_scan<16>(LGML_SCAN_ARGS);
+        default: return launch_scan<32>(LGML_SCAN_ARGS);
+    }
+#undef LGML_SCAN_ARGS
+}
+
+LGML_API int lgml_delta_output(const float *o, const float *weight, const float *gate, int ldg, void *out, int dtype, int ldo,
+                               int n_tokens, int H, int Dv, float eps, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && H > 0 && Dv > 0 && H <= 65535, "delta_output: bad sizes");
+    LGML_REQUIRE(ldg >= H * Dv && ldo >= H * Dv, "delta_output: a row stride is below H Dv");
+    if (n_tokens == 0) return 0;
+    dim3 grid(n_tokens, H);
+    if (dtype == LGML_F32)
+        lgml_launch(delta_output_kernel<float>, grid, 128, 0, stream, o, weight, gate, ldg, (float *)out, ldo, H, Dv, eps);
+    else if (dtype == LGML_BF16)
+        lgml_launch(delta_output_kernel<__nv_bfloat16>, grid, 128, 0, stream, o, weight, gate, ldg, (__nv_bfloat16 *)out, ldo, H, Dv, eps);
+    else
+        LGML_FAIL("delta_output: unknown type %d", dtype);
+    return lgml_launch_status("delta_output");
+}

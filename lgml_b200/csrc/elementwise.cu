@@ -455,6 +455,34 @@ LGML_API int lgml_silu_mul(const void *gu, void *act, int dtype, int n_tokens, i
 }
 
 // ---------------------------------------------------------------------------------------
+// y = relu(x)^2, element by element (the activation of a dense feed-forward), in place or not
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void relu_sq_kernel(const T *__restrict__ x, T *__restrict__ y, size_t total) {
+    pdl_trigger();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = fmaxf(to_f32(act_load(x + i)), 0.f);
+        y[i] = from_f32<T>(v * v);
+    }
+}
+
+LGML_API int lgml_relu_sq(const void *x, void *y, int dtype, long long total, cudaStream_t stream) {
+    LGML_REQUIRE(total >= 0, "relu_sq: bad size");
+    if (total == 0) return 0;
+    const int threads = 256;
+    const long long want = (total + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (dtype == LGML_F32)
+        lgml_launch(relu_sq_kernel<float>, blocks, threads, 0, stream, (const float *)x, (float *)y, (size_t)total);
+    else if (dtype == LGML_BF16)
+        lgml_launch(relu_sq_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16 *)x, (__nv_bfloat16 *)y, (size_t)total);
+    else
+        LGML_FAIL("relu_sq: unknown type %d", dtype);
+    return lgml_launch_status("relu_sq");
+}
+
+// ---------------------------------------------------------------------------------------
 // x[t, :] += delta[t, :]   (the residual sum in float32 when no norm follows)
 // ---------------------------------------------------------------------------------------
 template <typename TD>

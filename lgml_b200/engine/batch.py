@@ -58,6 +58,7 @@ class StepBatch:
         self.max_q_len = max(lens) if lens else 0
         self.max_kv_len = max(self.kv_lens) if lens else 0
         self.decode_splits = None       # a fixed split count (set by a captured graph)
+        self.shared = {}                # what one layer of this step keeps for later layers (by name)
         self._tiles = {}
         self.after_staged_copy = None   # called after a later copy out of the pinned buffer (its owner marks the buffer busy again)
 

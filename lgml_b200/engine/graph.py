@@ -39,6 +39,7 @@ class DecodeBatch:
         if reach:
             self.max_kv_len = min(self.max_kv_len, reach)       # the longest context of the steps this graph replays
         self.decode_splits = None
+        self.shared = {}                # what one layer of the step keeps for later layers (by name)
         total = 3 * S + (S + 1) + 4 * S + S * sum(self.widths)
         self.total = total
         self.dev = torch.zeros(total, dtype=torch.int32, device=device)

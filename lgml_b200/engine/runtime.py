@@ -108,6 +108,12 @@ class Runtime:
                                            out, n_heads, scale, window, self.status, softcap=softcap)
         return ops.paged_attention(q, batch, cache, out, n_heads, scale, window, self.status)
 
+    def sink_attention(self, q, batch, cache, out, n_heads: int, scale: float, window: int, slopes, sinks, gate) -> torch.Tensor:
+        """Attention with a sink, distance slopes, a window and an output gate (keys and values
+        with head sizes of their own) of the step's queries over the cache."""
+        return ops.sink_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
+                                  window, self.status, slopes=slopes, sinks=sinks, gate=gate)
+
     # ---- faults ------------------------------------------------------------------------
     def check_status(self, code: Optional[int] = None) -> None:
         """Raise if a kernel flagged a fault; ``code`` is the status word when the caller

@@ -2,6 +2,7 @@
 from ..config import lookup_architecture
 from .decoder import DecoderModel, LayerCall
 from . import llama  # noqa: F401  (registers LlamaForCausalLM)
+from . import lefulorn  # noqa: F401  (registers Lefulorn)
 
 
 def build_model(config):

@@ -251,6 +251,17 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, paired: bool = False) -> 
     return out
 
 
+def relu_sq(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = relu(x)^2 element by element (in place when ``out`` is None)."""
+    _need(x, "activation input")
+    out = x if out is None else out
+    if out.shape != x.shape or out.dtype != x.dtype or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("relu_sq: input and output must be contiguous and alike")
+    fn = _fn("elementwise", "lgml_relu_sq", [c_void_p, c_void_p, c_int, c_longlong, c_void_p])
+    _check("elementwise", fn(_ptr(x), _ptr(out), dtype_code(x.dtype), x.numel(), _stream()), "relu_sq")
+    return out
+
+
 def residual_add(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     """x += delta, the sum in float32."""
     _need(x, "residual stream", torch.float32)
@@ -412,6 +423,170 @@ def paged_attention_ref(q: torch.Tensor, positions: torch.Tensor, seq_of_token: 
     _check("attention_ref", fn(_ptr(q), dtype_code(q.dtype), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1],
                                _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(out), ldo, n, n_heads, hkv, d, float(scale), int(window or 0),
                                float(softcap or 0.0), _ptr(status), _stream()), "paged_attention_ref")
+    return out
+
+
+def sink_qkv_store(proj: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                   k_pages: torch.Tensor, v_pages: torch.Tensor, n_heads: int, status: torch.Tensor, temp_coef: float = 0.0,
+                   temp_every: int = 1, v_mode: int = 0, v_keep: Optional[torch.Tensor] = None,
+                   v_lambda: Optional[torch.Tensor] = None, write_kv: bool = True) -> torch.Tensor:
+    """From the fused projection's float32 output ``proj`` [tokens, q | k | v | ...]: q times its
+    position's temperature 1 + coef ln(floor((p + 1) / every) + 1) into a buffer of the cache's
+    type (returned, [tokens, H D]); k and v into their cells.  ``v_mode`` 1 also keeps v in
+    ``v_keep`` (float32 [tokens, Hkv Dv]); 2 stores (1 - lambda) v + lambda v_keep instead of v."""
+    _need(proj, "projection output", torch.float32, 2)
+    _need(k_pages, "key pages", ndim=4)
+    _need(v_pages, "value pages", k_pages.dtype, 4)
+    ldp = _rows_contiguous(proj, "projection output")
+    n = proj.shape[0]
+    n_pages, hkv, page, d = k_pages.shape
+    dv = v_pages.shape[3]
+    if v_pages.shape[:3] != k_pages.shape[:3] or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise KernelError(f"sink_qkv_store: key pages {tuple(k_pages.shape)} and value pages {tuple(v_pages.shape)} do not go together")
+    if proj.shape[1] < n_heads * d + hkv * (d + dv):
+        raise KernelError(f"sink_qkv_store: {proj.shape[1]} columns do not hold q, k and v")
+    _need(positions, "positions", torch.int32, 1)
+    _need(seq_of_token, "request index of tokens", torch.int32, 1)
+    _need(block_table, "block table", torch.int32, 2)
+    if positions.numel() != n or seq_of_token.numel() != n or not block_table.is_contiguous():
+        raise KernelError("sink_qkv_store: one position and one request index per token, and a contiguous block table")
+    if v_mode:
+        _need(v_keep, "kept values", torch.float32, 2)
+        if tuple(v_keep.shape) != (n, hkv * dv) or not v_keep.is_contiguous():
+            raise KernelError(f"sink_qkv_store: kept values must be a contiguous [{n}, {hkv * dv}]")
+    if v_mode == 2:
+        _need(v_lambda, "mixing weight", torch.float32)
+    q_out = torch.empty((n, n_heads * d), dtype=k_pages.dtype, device=proj.device)
+    fn = _fn("attention_sink", "lgml_sink_qkv_store", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                                       c_void_p, c_int, c_void_p, c_void_p])
+    _check("attention_sink", fn(_ptr(proj), ldp, _ptr(q_out), dtype_code(k_pages.dtype), q_out.stride(0), _ptr(positions), _ptr(seq_of_token),
+                                _ptr(block_table), block_table.shape[1], _ptr(k_pages), _ptr(v_pages), n_pages, page, n, n_heads, hkv, d, dv,
+                                float(temp_coef), int(temp_every), int(v_mode), _ptr(v_keep), _ptr(v_lambda), 1 if write_kv else 0,
+                                _ptr(status), _stream()), "sink_qkv_store")
+    return q_out
+
+
+def sink_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                   k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
+                   status: torch.Tensor, slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
+                   gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t, h] = sum_j w_j v_j over the request's keys at positions p - window < j <= p (all j <= p
+    when window is 0), w_j = exp(s_j) / (exp(sink_h) + sum exp(s)), s_j = (q . k_j) scale - slope_h (p - j);
+    then times sigmoid(gate[t, h]) element by element when ``gate`` (float32, pre-sigmoid; may be a
+    column slice) is given.  Keys have head size D, values Dv."""
+    _need(q, "queries", ndim=2)
+    _need(out, "attention output", q.dtype, 2)
+    ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
+    n = q.shape[0]
+    _need(k_pages, "key pages", q.dtype, 4)
+    _need(v_pages, "value pages", q.dtype, 4)
+    n_pages, hkv, page, d = k_pages.shape
+    dv = v_pages.shape[3]
+    _need(positions, "positions", torch.int32, 1)
+    _need(seq_of_token, "request index of tokens", torch.int32, 1)
+    _need(block_table, "block table", torch.int32, 2)
+    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * dv):
+        raise KernelError(f"sink_attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {n_heads} heads of {d} and {dv}")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
+        raise KernelError("sink_attention: pages and block table must be contiguous")
+    for t, what in ((slopes, "slopes"), (sinks, "sinks")):
+        if t is not None:
+            _need(t, what, torch.float32, 1)
+            if t.numel() != n_heads or not t.is_contiguous():
+                raise KernelError(f"sink_attention: one of the {what} per head")
+    ldg = 0
+    if gate is not None:
+        _need(gate, "gate", torch.float32, 2)
+        ldg = _rows_contiguous(gate, "gate")
+        if tuple(gate.shape) != (n, n_heads * dv):
+            raise KernelError(f"sink_attention: gate {tuple(gate.shape)} is not [{n}, {n_heads * dv}]")
+    fn = _fn("attention_sink", "lgml_sink_attention", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                                       c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                       c_float, c_int, c_void_p, c_void_p])
+    _check("attention_sink", fn(_ptr(q), dtype_code(q.dtype), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1],
+                                _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), ldo, n, n_heads,
+                                hkv, d, dv, float(scale), int(window or 0), _ptr(status), _stream()), "sink_attention")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# the gated delta rule
+# ----------------------------------------------------------------------------------------
+
+def delta_prepare(proj: torch.Tensor, a_pre: torch.Tensor, conv_w: torch.Tensor, state: torch.Tensor, conv_off: int,
+                  seq_of_token: torch.Tensor, seq_start: torch.Tensor, slots: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                  n_heads: int, n_kv_heads: int, dim: int, vdim: int):
+    """Everything of a delta-rule mixer that tokens can do side by side.  ``proj`` float32
+    [tokens, q (G D) | k (G D) | v (H Dv) | beta (H) | ...]; ``a_pre`` float32 [tokens, H D];
+    ``conv_w`` float32 [2 G D + H Dv, taps]; ``state`` float32 [slots, floats] whose part from
+    ``conv_off`` on holds each request's last taps - 1 convolution inputs (updated here).
+    Returns (q | k | v after convolution, SiLU and the norms [tokens, C], beta [tokens, H], decay [tokens, H D])."""
+    _need(proj, "projection output", torch.float32, 2)
+    _need(a_pre, "decay input", torch.float32, 2)
+    _need(conv_w, "convolution weights", torch.float32, 2)
+    _need(state, "state slots", torch.float32, 2)
+    for t, what in ((seq_of_token, "request index of tokens"), (seq_start, "first tokens of requests"), (slots, "slots")):
+        _need(t, what, torch.int32, 1)
+    _need(a_log, "decay rates", torch.float32, 1)
+    _need(dt_bias, "decay bias", torch.float32, 1)
+    ldp, lda = _rows_contiguous(proj, "projection output"), _rows_contiguous(a_pre, "decay input")
+    n, S = proj.shape[0], slots.numel()
+    C = 2 * n_kv_heads * dim + n_heads * vdim
+    taps = conv_w.shape[1]
+    if conv_w.shape[0] != C or not conv_w.is_contiguous() or not state.is_contiguous():
+        raise KernelError(f"delta_prepare: convolution weights {tuple(conv_w.shape)} do not fit {C} channels")
+    if proj.shape[1] < C + n_heads or a_pre.shape != (n, n_heads * dim) or a_log.numel() != n_heads or dt_bias.numel() != n_heads * dim:
+        raise KernelError("delta_prepare: shapes disagree")
+    if seq_of_token.numel() != n or seq_start.numel() != S + 1 or state.shape[1] < conv_off + (taps - 1) * C:
+        raise KernelError("delta_prepare: the batch's description or the state's size does not fit")
+    out_c = torch.empty((n, C), dtype=torch.float32, device=proj.device)
+    beta = torch.empty((n, n_heads), dtype=torch.float32, device=proj.device)
+    decay = torch.empty((n, n_heads * dim), dtype=torch.float32, device=proj.device)
+    fn = _fn("delta_rule", "lgml_delta_prepare", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p,
+                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                  c_int, c_int, c_void_p])
+    _check("delta_rule", fn(_ptr(proj), ldp, _ptr(a_pre), lda, _ptr(conv_w), taps, _ptr(state), state.stride(0), int(conv_off), _ptr(seq_of_token),
+                            _ptr(seq_start), _ptr(slots), _ptr(a_log), _ptr(dt_bias), _ptr(out_c), _ptr(beta), _ptr(decay), n, S, n_heads,
+                            n_kv_heads, dim, vdim, _stream()), "delta_prepare")
+    return out_c, beta, decay
+
+
+def delta_scan(qkv_c: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, seq_start: torch.Tensor,
+               slots: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """The recurrence S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q over each request's
+    tokens in order, from and into its slot of ``state`` (S of head h at floats [h D Dv, (h + 1) D Dv)).
+    Returns o float32 [tokens, H Dv]."""
+    n = qkv_c.shape[0]
+    for t, what in ((qkv_c, "prepared q, k, v"), (beta, "beta"), (decay, "decay")):
+        _need(t, what, torch.float32, 2)
+        if not t.is_contiguous() or t.shape[0] != n:
+            raise KernelError(f"delta_scan: {what} must be contiguous with one row per token")
+    _need(state, "state slots", torch.float32, 2)
+    if qkv_c.shape[1] != 2 * n_kv_heads * dim + n_heads * vdim or beta.shape[1] != n_heads or decay.shape[1] != n_heads * dim \
+            or state.shape[1] < n_heads * dim * vdim or not state.is_contiguous():
+        raise KernelError("delta_scan: shapes disagree")
+    o = torch.empty((n, n_heads * vdim), dtype=torch.float32, device=qkv_c.device)
+    fn = _fn("delta_rule", "lgml_delta_scan", [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                               c_int, c_int, c_int, c_void_p])
+    _check("delta_rule", fn(_ptr(qkv_c), _ptr(beta), _ptr(decay), _ptr(state), state.stride(0), _ptr(seq_start), _ptr(slots), _ptr(o),
+                            slots.numel(), n_heads, n_kv_heads, dim, vdim, _stream()), "delta_scan")
+    return o
+
+
+def delta_output(o: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, eps: float, out_dtype: torch.dtype, n_heads: int) -> torch.Tensor:
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * sigmoid(gate[t, h]) per head of size Dv = len(weight)."""
+    _need(o, "read-out", torch.float32, 2)
+    _need(weight, "norm weight", torch.float32, 1)
+    _need(gate, "gate", torch.float32, 2)
+    n, dv = o.shape[0], weight.numel()
+    ldg = _rows_contiguous(gate, "gate")
+    if o.shape[1] != n_heads * dv or tuple(gate.shape) != (n, n_heads * dv) or not o.is_contiguous():
+        raise KernelError("delta_output: shapes disagree")
+    out = torch.empty((n, n_heads * dv), dtype=out_dtype, device=o.device)
+    fn = _fn("delta_rule", "lgml_delta_output", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check("delta_rule", fn(_ptr(o), _ptr(weight), _ptr(gate), ldg, _ptr(out), dtype_code(out_dtype), out.stride(0), n, n_heads, dv, float(eps),
+                            _stream()), "delta_output")
     return out
 
 

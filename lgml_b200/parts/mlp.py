@@ -1,4 +1,4 @@
-"""The gated feed-forward: down(act(gate(h)) * up(h)) with act = SiLU
+"""Feed-forward parts.  The gated one: down(act(gate(h)) * up(h)) with act = SiLU
 (``lua/lgml/transformer.lua:2047-2049``; silu(a) = a * sigmoid(a),
 ``src/lgml.c:1476-1482``).  Gate and up are one fused product: the two matrices
 are concatenated row-wise when they are bound, gate first."""
@@ -58,4 +58,36 @@ class GatedMLP(Part):
         return rt.linear(act, self.wd, bias=self.bd, partials_ok=True)
 
 
+class DenseMLP(Part):
+    """The dense feed-forward down(act(up(h) + b_up)) + b_down with act = relu squared."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, inner: int, activation: str = "relu2", bias: bool = True):
+        if activation != "relu2":
+            raise ValueError(f"activation '{activation}' is not supported (only 'relu2')")
+        self.width, self.inner, self.bias = width, inner, bool(bias)
+        self.wu = self.bu = self.wd = self.bd = None
+
+    def tensor_specs(self, prefix):
+        E, F = self.width, self.inner
+        specs = [TensorSpec(prefix + ".up", (F, E)), TensorSpec(prefix + ".down", (E, F))]
+        if self.bias:
+            specs += [TensorSpec(prefix + ".up.b", (F,), VECTOR), TensorSpec(prefix + ".down.b", (E,), VECTOR)]
+        return specs
+
+    def bind(self, prefix, tensors, rt):
+        self.wu, self.wd = tensors[prefix + ".up"], tensors[prefix + ".down"]
+        if self.bias:
+            self.bu, self.bd = tensors[prefix + ".up.b"], tensors[prefix + ".down.b"]
+
+    def first_weights(self):
+        return [self.wu]
+
+    def forward(self, rt, h):
+        act = ops.relu_sq(rt.linear(h, self.wu, bias=self.bu))
+        return rt.linear(act, self.wd, bias=self.bd, partials_ok=True)
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "dense_mlp", DenseMLP)

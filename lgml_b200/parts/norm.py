@@ -12,16 +12,17 @@ from .base import Part, register_part
 
 class RMSNorm(Part):
     graph_safe = True
-    def __init__(self, width: int, eps: float):
+    def __init__(self, width: int, eps: float, suffix: str = ".weight"):
         self.width = width
         self.eps = float(eps)
+        self.suffix = suffix        # what the weight's name adds to the part's prefix ("" when the prefix is the name)
         self.weight = None
 
     def tensor_specs(self, prefix):
-        return [TensorSpec(prefix + ".weight", (self.width,), VECTOR, init=(1.0, 1.0))]
+        return [TensorSpec(prefix + self.suffix, (self.width,), VECTOR, init=(1.0, 1.0))]
 
     def bind(self, prefix, tensors, rt):
-        self.weight = tensors[prefix + ".weight"]
+        self.weight = tensors[prefix + self.suffix]
 
     def forward(self, rt, x, out_dtype, delta=None, rows=None):
         """Norm of x (+ delta).  x is the float32 residual stream; with ``delta`` the sum
