@@ -16,8 +16,9 @@ measured copy bandwidth, and ``roofline_points`` the same fraction for every bat
 
 ``--shape llama32_3b`` runs that shape's own workload (32 prompts of 128 to 4,096 tokens in
 portions of 512 beside decodes, 512 new tokens each) through ``Engine.generate``;
-``--shape llama2_13b`` decodes at batch 16 after 3,584-token prompts; ``--cpu-baseline``
-times the plain CPU implementation at the tiny configurations.
+``--shape llama2_13b`` decodes at batch 16 after 3,584-token prompts; ``--design lefulorn``
+times that design beside the Llama decoder at equal layer sizes; ``--cpu-baseline`` times the
+plain CPU implementation at the tiny configurations.
 """
 from __future__ import annotations
 
@@ -278,6 +279,94 @@ def run_mixed_workload(shape_name, shape, args, warmup: int) -> dict:
     }
 
 
+# ---- another design beside the Llama decoder at equal layer sizes (--design) ---------------------
+
+def lefulorn_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, layers: int, window: int, vocab: int) -> dict:
+    """Lefulorn with layers of a real model's size: attention and channel-delta layers in turn, every one with its
+    dense feed-forward; keys and values of ``head_dim``; a window over the attention layers; ranks of 64."""
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+                                          "mask": {"size": window}, "q_temp": {"coef": 0.1, "every": 256}, "v_mix": True},
+           "mlp": {"kind": "dense", "ff": ff}}
+    dl = {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "conv": 4,
+                                             "rank_a": 64, "rank_g": 64}, "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Lefulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+            "layers": [dict(att if i % 2 == 0 else dl) for i in range(layers)]}
+
+
+DESIGN_SIZES = {          # name -> width, heads, KV heads, head size, dense inner width, layers
+    "w2048": (2048, 16, 4, 128, 8192, 4),
+    "w4096": (4096, 32, 8, 128, 14336, 4),
+}
+
+
+def run_design_compare(args, warmup: int) -> dict:
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 after 2,048-token prompts) of the
+    Lefulorn design and of the Llama decoder with layers of the same sizes (the gated feed-forward's inner width
+    is two thirds of the dense one's: the same number of weights), random weights, with the device time of every
+    kernel class in one prefill step and one decode step of each."""
+    import torch
+
+    import lgml_b200
+    from lgml_b200 import ops
+    from lgml_b200.config import config_from_dict
+    from lgml_b200.engine.runner import ModelRunner
+
+    global BATCH, PROMPT_LEN, CONTEXT, PREFILL_TOKENS
+    BATCH, PROMPT_LEN, PREFILL_TOKENS = args.batch or 8, args.prompt_len or 2048, args.prefill_tokens or 2048
+    CONTEXT = -(-(max(PROMPT_LEN, PREFILL_TOKENS) + args.steps + 2 * warmup + 128) // 64) * 64
+    window, vocab = 1024, 32000
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    clocks = ClockSampler()
+    clocks.start()
+    out = {}
+    for name, (E, H, G, D, F, L) in DESIGN_SIZES.items():
+        llama = {**LLAMA31_8B, "num_hidden_layers": L, "hidden_size": E, "num_attention_heads": H, "num_key_value_heads": G, "head_dim": D,
+                 "intermediate_size": (2 * F // 3 + 255) // 256 * 256, "vocab_size": vocab, "max_position_embeddings": CONTEXT}
+        row = {}
+        for design, d in (("lefulorn", lefulorn_shape(E, H, G, D, F, L, window, vocab)), ("llama", llama)):
+            cfg = config_from_dict(d)
+            runner = ModelRunner.from_config(cfg, seed=0, dtype=torch.bfloat16, n_pages=BATCH * (CONTEXT // 64) + 8, max_slots=BATCH,
+                                             max_step_tokens=2048)
+            prefill_ms = run_prefill(runner, cfg)
+            ms_step, _, launches = run_decode(runner, cfg, BATCH, args.steps, warmup)
+            # kernel classes: one prompt step and one decode step, eagerly, events around every launch
+            g = torch.Generator().manual_seed(9)
+            reqs = [runner.open(("classes", i)) for i in range(BATCH)]
+            try:
+                ids = [torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist() for _ in reqs]
+                for r, t in zip(reqs[1:], ids[1:]):
+                    runner.step([(r, t, [])])
+                with ops.KernelTimes() as kt:
+                    runner.step([(reqs[0], ids[0], [PROMPT_LEN - 1])])
+                pre_us = {k: round(v, 1) for k, v in kt.totals().items() if not k.endswith(" calls")}
+                toks = [[int(t)] for t in torch.randint(0, cfg.vocab_size, (BATCH,), generator=g)]
+                runner.step([(r, t, [0]) for r, t in zip(reqs, toks)])
+                with ops.KernelTimes() as kt:
+                    for _ in range(3):
+                        runner.step([(r, t, [0]) for r, t in zip(reqs, toks)])
+                dec_us = {k: round(v / 3.0, 1) for k, v in kt.totals().items() if not k.endswith(" calls")}
+            finally:
+                for r in reqs:
+                    runner.close(r)
+            row[design] = {"prefill_tok_s": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "prefill_ms": round(prefill_ms, 3),
+                           "decode_tok_s": round(BATCH * 1000.0 / ms_step, 1), "decode_ms_per_step": round(ms_step, 4),
+                           "decode_launches": int(launches), "kernel_us_prefill_step": pre_us, "kernel_us_decode_step": dec_us}
+            del runner
+            torch.cuda.empty_cache()
+        out[name] = row
+    clock_rec = clocks.stop()
+    first = next(iter(out.values()))["lefulorn"]
+    return {"metric": f"Lefulorn beside the Llama decoder at equal layer sizes: prefill of {PREFILL_TOKENS:,} tokens and decode at batch {BATCH}",
+            "value": first["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": first["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic: random weights N(0, 0.02), uniform-random token ids",
+            "config": {"sizes": {k: dict(zip(("width", "heads", "kv_heads", "head_dim", "dense_ff", "layers"), v)) for k, v in DESIGN_SIZES.items()},
+                       "window": window, "vocab": vocab, "global_batch": BATCH, "prompt_len": PROMPT_LEN, "seq_len": CONTEXT,
+                       "parallelism": "single GPU", "peaks": peak_src, "hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops},
+            "clocks": clock_rec, "designs": out, "gpu_launches": int(ops.launch_count()),
+            "kernel_libraries": lgml_b200.csrc.loaded_libraries()}
+
+
 def run_cpu_baseline() -> dict:
     """The stated CPU baseline: the plain float64 implementation under ``tests/plain`` (whole
     sequences, no cache) on the host, at the two tiny configurations: tokens per second of a
@@ -321,6 +410,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0, help="context (tokens a request may hold) instead of the shape's own")
     ap.add_argument("--prefill-tokens", type=int, default=0, help="tokens of the timed prompt instead of 2,048 (read in portions of 2,048)")
     ap.add_argument("--no-kernel-times", action="store_true", help="leave out the per-kernel-class times of a decode step")
+    ap.add_argument("--design", default="", choices=["", "lefulorn"], help="time this design beside the Llama decoder at equal layer sizes "
+                    "(prefill and decode, with kernel-class times) instead of the headline workload")
     ap.add_argument("--cpu-baseline", action="store_true", help="time the plain CPU implementation at the tiny configurations and stop")
     args = ap.parse_args()
     if args.cpu_baseline:
@@ -358,6 +449,9 @@ def main() -> int:
     # the others' portions, so every request gets this many new tokens more than the turns that are timed
     prompt_turns = -(-BATCH * PROMPT_LEN // 2048)
     CONTEXT = -(-max(CONTEXT, PROMPT_LEN + args.steps + 64 + prompt_turns, PREFILL_TOKENS) // 64) * 64
+    if args.design:
+        print(json.dumps(run_design_compare(args, warmup)))
+        return 0
     if args.shape == "llama32_3b" and not args.decode_only:
         print(json.dumps(run_mixed_workload(shape_name, shape, args, warmup)))
         return 0

@@ -147,6 +147,231 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
         out[(size_t)t * ldo + (size_t)h * Dv + d] = from_f32<T>(o);
     }
 }
+
+// ---------------------------------------------------------------------------------------------
+// Prompts and portions, bfloat16, on tensor cores (mma.sync m16n8k16, float32 accumulation).
+// A CTA of four warps takes a tile of up to 64 consecutive tokens of one request and one head; a
+// warp owns 16 query rows.  The keys are walked a page (64 keys) at a time, only the pages the
+// tile's window reaches: S = Q K^T with Q as the A operand (fragments held in registers for the
+// whole walk) and the page's keys as B; scale, distance bias and the causal/window mask on the
+// accumulators; a running maximum and sum per row; P, rounded to bfloat16, goes straight from
+// the accumulators' layout into the A operand of O += P V.  At the end the sink joins the
+// denominator, and the gate multiplies the output.  KS = key size / 16 and NV = value size / 8
+// (both rounded up; the padding is zeros in shared memory).
+// ---------------------------------------------------------------------------------------------
+constexpr int TILE_Q = 64;
+constexpr int PAGE = 64;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// rows x width elements from global (row r at src + r * ld... given by row_ptr(r), null: zeros) into
+// shared rows of `lds` elements, zero-padded to `padded` columns; 16-byte loads when `vec`
+template <typename RowPtr>
+__device__ __forceinline__ void load_rows(__nv_bfloat16 *dst, int lds, int rows, int width, int padded, bool vec, RowPtr row_ptr) {
+    const int chunks = padded / 8;
+    for (int c = threadIdx.x; c < rows * chunks; c += blockDim.x) {
+        const int r = c / chunks, col = (c - r * chunks) * 8;
+        const __nv_bfloat16 *src = row_ptr(r);
+        uint4 val = make_uint4(0u, 0u, 0u, 0u);
+        if (src != nullptr) {
+            if (vec && col + 8 <= width) {
+                val = act_load(reinterpret_cast<const uint4 *>(src + col));
+            } else {
+                __nv_bfloat16 *e = reinterpret_cast<__nv_bfloat16 *>(&val);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (col + j < width) e[j] = act_load(src + col + j);
+            }
+        }
+        *reinterpret_cast<uint4 *>(dst + (size_t)r * lds + col) = val;
+    }
+}
+
+template <int KS, int NV>
+__global__ void __launch_bounds__(128) sink_attention_mma_kernel(
+    const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ tiles,
+    const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
+    const __nv_bfloat16 *__restrict__ v_pages, int n_pages, const float *__restrict__ slopes, const float *__restrict__ sinks,
+    const float *__restrict__ gate, int ldg, __nv_bfloat16 *__restrict__ out, int ldo, int H, int Hkv, int D, int Dv, float scale,
+    int window, int *__restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int DP = KS * 16, DVP = NV * 8;
+    constexpr int LDK = DP + 8, LDV = DVP + 8;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(smem_raw);
+    __nv_bfloat16 *Ks = Qs + TILE_Q * LDK;
+    __nv_bfloat16 *Vs = Ks + PAGE * LDK;
+    const int tile = blockIdx.x, h = blockIdx.y;
+    const int g = h / (H / Hkv);
+    const int seq = tiles[tile * 4], row0 = tiles[tile * 4 + 1], n_tok = tiles[tile * 4 + 2];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int mat = lane >> 3, mrow = lane & 7;
+    const int p0 = positions[row0];                       // the tile's tokens stand at p0, p0 + 1, ...
+    const int p_last = p0 + n_tok - 1;
+    const int lo_key = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+    const int *table = block_table + (size_t)seq * max_blocks;
+    const bool vec_k = (D % 8 == 0) && (ldq % 8 == 0) && ((reinterpret_cast<uintptr_t>(q) & 15) == 0);
+    const bool vec_v = (Dv % 8 == 0);
+    const float LOG2E = 1.4426950408889634f;
+    const float slope2 = (slopes ? slopes[h] : 0.f) * LOG2E, scale2 = scale * LOG2E;
+
+    load_rows(Qs, LDK, TILE_Q, D, DP, vec_k, [&](int r) { return r < n_tok ? q + (size_t)(row0 + r) * ldq + (size_t)h * D : nullptr; });
+    __syncthreads();
+    uint32_t qf[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) ldmatrix_x4(qf[ks], Qs + (size_t)(warp * 16 + (mat & 1) * 8 + mrow) * LDK + ks * 16 + (mat >> 1) * 8);
+
+    // this thread's two rows of the warp's 16: r0 = lane / 4 and r0 + 8
+    const int qr[2] = {warp * 16 + (lane >> 2), warp * 16 + (lane >> 2) + 8};
+    const int qpos[2] = {p0 + qr[0], p0 + qr[1]};
+    const bool qok[2] = {qr[0] < n_tok, qr[1] < n_tok};
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float oacc[NV][4];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+
+    for (int pg = lo_key / PAGE; pg <= p_last / PAGE; ++pg) {
+        const int page = pg < max_blocks ? table[pg] : -1;
+        const bool have = page >= 0 && page < n_pages;
+        if (!have && threadIdx.x == 0) atomicExch(status, 3);
+        __syncthreads();            // everyone is done with the page before
+        const size_t cell0 = ((size_t)(have ? page : 0) * Hkv + g) * PAGE;
+        load_rows(Ks, LDK, PAGE, D, DP, vec_k && (D % 8 == 0), [&](int r) { return have ? k_pages + (cell0 + r) * D : nullptr; });
+        load_rows(Vs, LDV, PAGE, Dv, DVP, vec_v, [&](int r) { return have ? v_pages + (cell0 + r) * Dv : nullptr; });
+        __syncthreads();
+        // the warp's rows see keys up to their own positions: skip a page that lies wholly outside
+        const int w_first = p0 + warp * 16, w_last = min(w_first + 15, p_last);
+        const int key0 = pg * PAGE;
+        if (warp * 16 >= n_tok || key0 > w_last || (window > 0 && key0 + PAGE - 1 < w_first - window + 1)) continue;
+
+        float sacc[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {       // two key tiles of 8 per ldmatrix
+                uint32_t b[4];
+                ldmatrix_x4(b, Ks + (size_t)(np * 16 + (mat >> 1) * 8 + mrow) * LDK + ks * 16 + (mat & 1) * 8);
+                mma_bf16(sacc[2 * np], qf[ks], b[0], b[1]);
+                mma_bf16(sacc[2 * np + 1], qf[ks], b[2], b[3]);
+            }
+        }
+        // scale, distance bias, mask; scores in the base-2 domain
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int rr = i >> 1;
+                const int j = key0 + nt * 8 + (lane & 3) * 2 + (i & 1);
+                const int dist = qpos[rr] - j;
+                const bool ok = qok[rr] && dist >= 0 && (window == 0 || dist < window);
+                const float sv = ok ? sacc[nt][i] * scale2 - slope2 * (float)dist : -INFINITY;
+                sacc[nt][i] = sv;
+                mx[rr] = fmaxf(mx[rr], sv);
+            }
+        float corr[2];
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+            mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+            const float m_new = fmaxf(m_run[rr], mx[rr]);
+            corr[rr] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[rr] - m_new);
+            m_run[rr] = m_new;
+            l_run[rr] *= corr[rr];
+        }
+        uint32_t pf[4][4];           // P as A fragments: key step kk covers key tiles 2 kk and 2 kk + 1
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            float pv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int rr = i >> 1;
+                pv[i] = (m_run[rr] == -INFINITY) ? 0.f : exp2f(sacc[nt][i] - m_run[rr]);
+            }
+            const uint32_t lo = pack_bf16(pv[0], pv[1]), hi = pack_bf16(pv[2], pv[3]);
+            // the sums run over the weights as the product sees them (rounded to bfloat16)
+            const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162 *>(&lo), hi2 = *reinterpret_cast<const __nv_bfloat162 *>(&hi);
+            l_run[0] += __bfloat162float(lo2.x) + __bfloat162float(lo2.y);
+            l_run[1] += __bfloat162float(hi2.x) + __bfloat162float(hi2.y);
+            pf[nt >> 1][(nt & 1) * 2] = lo;
+            pf[nt >> 1][(nt & 1) * 2 + 1] = hi;
+        }
+#pragma unroll
+        for (int nv = 0; nv < NV; ++nv) {
+            oacc[nv][0] *= corr[0];
+            oacc[nv][1] *= corr[0];
+            oacc[nv][2] *= corr[1];
+            oacc[nv][3] *= corr[1];
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+            for (int np = 0; np < NV / 2; ++np) {   // two value tiles of 8 per ldmatrix
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, Vs + (size_t)(kk * 16 + (mat & 1) * 8 + mrow) * LDV + np * 16 + (mat >> 1) * 8);
+                mma_bf16(oacc[2 * np], pf[kk], b[0], b[1]);
+                mma_bf16(oacc[2 * np + 1], pf[kk], b[2], b[3]);
+            }
+        }
+    }
+    // the sink joins the denominator; the quad's partial sums are added up
+    const float sink2 = sinks ? sinks[h] * LOG2E : -INFINITY;
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 1);
+        l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 2);
+        const float m_all = fmaxf(m_run[rr], sink2);
+        const float f = (m_run[rr] == -INFINITY) ? 0.f : exp2f(m_run[rr] - m_all);
+        const float den = l_run[rr] * f + (sinks ? exp2f(sink2 - m_all) : 0.f);
+        const float inv = den > 0.f ? f / den : 0.f;
+        if (!qok[rr]) continue;
+        const size_t t = (size_t)(row0 + qr[rr]);
+#pragma unroll
+        for (int nv = 0; nv < NV; ++nv)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int d = nv * 8 + (lane & 3) * 2 + e;
+                if (d >= Dv) continue;
+                float o = oacc[nv][rr * 2 + e] * inv;
+                if (gate) o *= 1.0f / (1.0f + __expf(-act_load(gate + t * ldg + (size_t)h * Dv + d)));
+                out[t * ldo + (size_t)h * Dv + d] = __float2bfloat16_rn(o);
+            }
+    }
+}
+
+template <int KS, int NV>
+int launch_mma(dim3 grid, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, const int *positions, const int *tiles, const int *block_table,
+               int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, const float *slopes, const float *sinks,
+               const float *gate, int ldg, __nv_bfloat16 *out, int ldo, int H, int Hkv, int D, int Dv, float scale, int window, int *status) {
+    const size_t smem = ((size_t)(TILE_Q + PAGE) * (KS * 16 + 8) + (size_t)PAGE * (NV * 8 + 8)) * 2;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(sink_attention_mma_kernel<KS, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LGML_FAIL("sink_attention_mma: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    lgml_launch(sink_attention_mma_kernel<KS, NV>, grid, 128, smem, stream, q, ldq, positions, tiles, block_table, max_blocks, k_pages, v_pages,
+                n_pages, slopes, sinks, gate, ldg, out, ldo, H, Hkv, D, Dv, scale, window, status);
+    return lgml_launch_status("sink_attention_mma");
+}
 }  // namespace
 
 // proj: float32 [n_tokens, ldp], columns q (H D) | k (Hkv D) | v (Hkv Dv) | anything else.
@@ -202,4 +427,35 @@ LGML_API int lgml_sink_attention(const void *q, int dtype, int ldq, const int *p
     else
         LGML_FAIL("sink_attention: unknown type %d", dtype);
     return lgml_launch_status("sink_attention");
+}
+
+// The tensor-core form for prompts and portions (bfloat16, pages of 64, head sizes up to 128).
+// tiles: int32 [n_tiles, 4] rows (request row, first token row, tokens <= 64, 0), each within one request.
+LGML_API int lgml_sink_attention_mma(const void *q, int ldq, const int *positions, const int *tiles, int n_tiles, const int *block_table,
+                                     int max_blocks, const void *k_pages, const void *v_pages, int n_pages, int page_size,
+                                     const float *slopes, const float *sinks, const float *gate, int ldg, void *out, int ldo, int H, int Hkv,
+                                     int D, int Dv, float scale, int window, int *status, cudaStream_t stream) {
+    LGML_REQUIRE(n_tiles >= 0 && H > 0 && Hkv > 0 && D > 0 && Dv > 0 && max_blocks > 0, "sink_attention_mma: bad sizes");
+    LGML_REQUIRE(page_size == PAGE, "sink_attention_mma: pages of %d tokens, this kernel takes %d", page_size, PAGE);
+    LGML_REQUIRE(H % Hkv == 0 && H <= 65535, "sink_attention_mma: %d heads on %d KV heads", H, Hkv);
+    LGML_REQUIRE(D <= 128 && Dv <= 128, "sink_attention_mma: head sizes %d and %d must be at most 128", D, Dv);
+    LGML_REQUIRE(window >= 0, "sink_attention_mma: bad window");
+    LGML_REQUIRE(gate == nullptr || ldg >= H * Dv, "sink_attention_mma: the gate's row stride %d is below H Dv", ldg);
+    if (n_tiles == 0) return 0;
+    dim3 grid(n_tiles, H);
+    const int ks = D <= 32 ? 2 : D <= 64 ? 4 : D <= 96 ? 6 : 8;
+    const int nv = Dv <= 32 ? 4 : Dv <= 64 ? 8 : Dv <= 96 ? 12 : 16;
+#define LGML_MMA_ARGS grid, stream, (const __nv_bfloat16 *)q, ldq, positions, tiles, block_table, max_blocks, (const __nv_bfloat16 *)k_pages, \
+                      (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, (__nv_bfloat16 *)out, ldo, H, Hkv, D, Dv, scale, window, status
+#define LGML_MMA_NV(KK) \
+    switch (nv) { case 4: return launch_mma<KK, 4>(LGML_MMA_ARGS); case 8: return launch_mma<KK, 8>(LGML_MMA_ARGS); \
+                  case 12: return launch_mma<KK, 12>(LGML_MMA_ARGS); default: return launch_mma<KK, 16>(LGML_MMA_ARGS); }
+    switch (ks) {
+        case 2: LGML_MMA_NV(2)
+        case 4: LGML_MMA_NV(4)
+        case 6: LGML_MMA_NV(6)
+        default: LGML_MMA_NV(8)
+    }
+#undef LGML_MMA_NV
+#undef LGML_MMA_ARGS
 }

@@ -130,7 +130,7 @@ struct Params {
     int tiles_a, tiles_b;   // tiles along the rows of A and of B; tile index = tile_b * tiles_a + tile_a
     int kb_per_split; // k blocks per grid.z slice
     int transposed;   // 1: the tile is y^T (A = weights, B = tokens)
-    int swiglu;       // 1: feature rows come in (gate, up) pairs; the output is silu(gate) * up, half as wide
+    int swiglu;       // 1: feature rows come in (gate, up) pairs; the output is silu(gate) * up, half as wide; 2: the output is relu(y)^2
     int out_f32;      // output element type
     int ldo;          // row stride of the output in elements
     long long split_stride;   // elements between the partial results of two splits (0: no split)
@@ -143,6 +143,8 @@ struct Params {
 // and division (a few units in the last place of float32, far below that rounding) instead of the
 // library's, which cost the epilogue of a 64-token tile more than its loads from tensor memory.
 __device__ __forceinline__ float silu_mul_fast(float gate, float up) { return __fdividef(gate, 1.0f + __expf(-gate)) * up; }
+// relu(y)^2, the activation of a dense feed-forward, for the epilogue that applies it in place of a pass of its own
+__device__ __forceinline__ float relu_sq(float y) { const float r = fmaxf(y, 0.f); return r * r; }
 
 // One thread's 16 consecutive features f0 .. f0 + 15 of token row a_row (tile row = token,
 // tile column = feature): bias, the gated activation if asked for, and the store.
@@ -152,7 +154,11 @@ __device__ __forceinline__ void store_run(const Params &p, int a_row, int f0, co
         float v[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) + ((p.bias && f0 + j < p.rows_b) ? p.bias[f0 + j] : 0.f);
-        if (p.swiglu) {
+        if (p.swiglu == 2) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = relu_sq(v[j]);
+        }
+        if (p.swiglu == 1) {
             // columns 2j and 2j+1 are the gate and the up of feature (f0 / 2) + j
             const size_t o = (size_t)a_row * p.ldo + (f0 >> 1);
             float act[8];
@@ -214,7 +220,7 @@ __device__ __forceinline__ void store_run_transposed(const Params &p, int a_row,
                                                      __nv_bfloat16 *out_h, bool f32) {
     const bool row_ok = a_row < p.rows_a;
     const float b = (p.bias && row_ok) ? p.bias[a_row] : 0.f;
-    if (p.swiglu) {
+    if (p.swiglu == 1) {
         // Lanes 2i and 2i+1 hold the gate and the up row of one feature.  Of every two tokens the
         // even lane finishes the first and the odd lane the second: one exchange for two tokens
         // (the even lane gives its gate of the second token, the odd lane its up of the first),
@@ -237,7 +243,8 @@ __device__ __forceinline__ void store_run_transposed(const Params &p, int a_row,
         for (int j = 0; j < 16; ++j) {
             const int token = token0 + j;
             if (token < p.rows_b) {
-                const float v = __uint_as_float(r[j]) + b;
+                float v = __uint_as_float(r[j]) + b;
+                if (p.swiglu == 2) v = relu_sq(v);
                 if (f32) out_f[(size_t)token * p.ldo + a_row] = v;
                 else out_h[(size_t)token * p.ldo + a_row] = __float2bfloat16_rn(v);
             }
@@ -919,15 +926,18 @@ LGML_API long long lgml_gemm_tcgen05_scratch_floats(int M, int N, int n_splits) 
 
 // y[M, N] = x[M, K] . w[N, K]^T (+ bias[N]);  x, w bfloat16 with row strides ldx, ldw (elements);
 // y bfloat16 or float32 with row stride ldy.  n_splits > 1 cuts K and needs `scratch`.
-// swiglu: the rows of w come in (gate, up) pairs and y[M, N / 2] = silu(gate) * up (no K split then).
+// swiglu = 1: the rows of w come in (gate, up) pairs and y[M, N / 2] = silu(gate) * up (no K split then);
+// swiglu = 2: y = relu(x . w^T + bias)^2 (no K split either).
 // reduce = 0 with n_splits > 1 leaves the partial sums [n_splits, M, N] in scratch for the next
 // kernel to add (bias is then not applied).
 LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, void *y, int y_f32, int M, int N, int K, int ldx,
                                int ldw, int ldy, int n_splits, float *scratch, int swiglu, int reduce, int *status,
                                cudaStream_t stream) {
     LGML_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
-    LGML_REQUIRE(ldx >= K && ldw >= K && ldy >= (swiglu ? N / 2 : N), "gemm_tcgen05: a leading dimension is smaller than its row");
-    LGML_REQUIRE(!swiglu || (N % 2 == 0 && n_splits == 1), "gemm_tcgen05: the gated epilogue needs an even N and no K split");
+    LGML_REQUIRE(swiglu >= 0 && swiglu <= 2, "gemm_tcgen05: unknown epilogue %d", swiglu);
+    LGML_REQUIRE(ldx >= K && ldw >= K && ldy >= (swiglu == 1 ? N / 2 : N), "gemm_tcgen05: a leading dimension is smaller than its row");
+    LGML_REQUIRE(!swiglu || n_splits == 1, "gemm_tcgen05: an epilogue with an activation takes no K split");
+    LGML_REQUIRE(swiglu != 1 || N % 2 == 0, "gemm_tcgen05: the gated epilogue needs an even N");
     LGML_REQUIRE(ldx % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: row strides (%d, %d) must be multiples of 8 elements (16 bytes) for TMA", ldx, ldw);
     LGML_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned for TMA");
     LGML_REQUIRE(n_splits >= 1 && n_splits <= 64, "gemm_tcgen05: bad split count %d", n_splits);

@@ -96,7 +96,7 @@ class Runtime:
             self._forked = False
 
     def fused_swiglu(self, x: torch.Tensor, w_pairs: torch.Tensor) -> bool:
-        """Whether the gated feed-forward can run its first product and activation as one kernel."""
+        """Whether a feed-forward can run its first product and its activation as one kernel."""
         return self.dtype == torch.bfloat16 and self.gemm_backend in ("auto", "tcgen05") and ops.tcgen05_supports(x, w_pairs)
 
     # ---- attention ---------------------------------------------------------------------
@@ -111,6 +111,12 @@ class Runtime:
     def sink_attention(self, q, batch, cache, out, n_heads: int, scale: float, window: int, slopes, sinks, gate) -> torch.Tensor:
         """Attention with a sink, distance slopes, a window and an output gate (keys and values
         with head sizes of their own) of the step's queries over the cache."""
+        if (self.dtype == torch.bfloat16 and self.attention_backend != "ref" and batch.max_q_len > ops.DECODE_MAX_Q
+                and cache.k.shape[2] == 64 and cache.k.shape[3] <= 128 and cache.v.shape[3] <= 128):
+            # prompts and portions: tiles of 64 tokens on tensor cores
+            tiles = batch.attention_tiles(ops.SINK_TILE_TOKENS)
+            return ops.sink_attention_mma(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window,
+                                          self.status, slopes=slopes, sinks=sinks, gate=gate)
         return ops.sink_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
                                   window, self.status, slopes=slopes, sinks=sinks, gate=gate)
 

@@ -510,6 +510,51 @@ def sink_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch
     return out
 
 
+SINK_TILE_TOKENS = 64      # query tokens per tile of the tensor-core sink attention
+
+
+def sink_attention_mma(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
+                       v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int, status: torch.Tensor,
+                       slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
+                       gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``sink_attention`` for prompts and portions on tensor cores: bfloat16, pages of 64, head sizes
+    up to 128.  ``tiles`` int32 [n_tiles, 4]: (request row, first token row, tokens <= 64, 0), each
+    tile within one request (``StepBatch.attention_tiles(SINK_TILE_TOKENS)``)."""
+    _need(q, "queries", torch.bfloat16, 2)
+    _need(out, "attention output", torch.bfloat16, 2)
+    ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
+    n = q.shape[0]
+    _need(k_pages, "key pages", torch.bfloat16, 4)
+    _need(v_pages, "value pages", torch.bfloat16, 4)
+    n_pages, hkv, page, d = k_pages.shape
+    dv = v_pages.shape[3]
+    _need(positions, "positions", torch.int32, 1)
+    _need(tiles, "tiles", torch.int32, 2)
+    _need(block_table, "block table", torch.int32, 2)
+    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * dv) or tiles.shape[1] != 4:
+        raise KernelError(f"sink_attention_mma: q {tuple(q.shape)} / out {tuple(out.shape)} / tiles {tuple(tiles.shape)} do not fit")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous() or not tiles.is_contiguous():
+        raise KernelError("sink_attention_mma: pages, block table and tiles must be contiguous")
+    for t, what in ((slopes, "slopes"), (sinks, "sinks")):
+        if t is not None:
+            _need(t, what, torch.float32, 1)
+            if t.numel() != n_heads or not t.is_contiguous():
+                raise KernelError(f"sink_attention_mma: one of the {what} per head")
+    ldg = 0
+    if gate is not None:
+        _need(gate, "gate", torch.float32, 2)
+        ldg = _rows_contiguous(gate, "gate")
+        if tuple(gate.shape) != (n, n_heads * dv):
+            raise KernelError(f"sink_attention_mma: gate {tuple(gate.shape)} is not [{n}, {n_heads * dv}]")
+    fn = _fn("attention_sink", "lgml_sink_attention_mma", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                                           c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                           c_float, c_int, c_void_p, c_void_p])
+    _check("attention_sink", fn(_ptr(q), ldq, _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(block_table), block_table.shape[1], _ptr(k_pages),
+                                _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), ldo, n_heads, hkv, d, dv,
+                                float(scale), int(window or 0), _ptr(status), _stream()), "sink_attention_mma")
+    return out
+
+
 # ----------------------------------------------------------------------------------------
 # the gated delta rule
 # ----------------------------------------------------------------------------------------
@@ -732,7 +777,7 @@ def _tcgen05_splits(M: int, N: int, K: int) -> int:
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], bias: Optional[torch.Tensor], status: torch.Tensor,
                  n_splits: Optional[int] = None, scratch: Optional[torch.Tensor] = None, swiglu: bool = False,
-                 partials_ok: bool = False, checked: bool = False):
+                 partials_ok: bool = False, checked: bool = False, relu_sq: bool = False):
     """out[M,N] = x[M,K] . w[N,K]^T (+ bias) on tcgen05 tensor cores; bfloat16 in, float32
     accumulation, out bfloat16 or float32.  ``swiglu``: the rows of w (and bias) come in
     (gate, up) pairs and out[M, N/2] = silu(gate) * up.  ``partials_ok``: when K is cut, return
@@ -752,8 +797,10 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
         _need(bias, "gemm bias", torch.float32, 1)
         if bias.numel() != N:
             raise KernelError("gemm_tcgen05: bias length is not N")
+    if swiglu and relu_sq:
+        raise KernelError("gemm_tcgen05: one activation at a time")
     if n_splits is None:
-        n_splits = 1 if swiglu else tcgen05_splits(M, N, K)
+        n_splits = 1 if (swiglu or relu_sq) else tcgen05_splits(M, N, K)
     elif checked:
         pass
     elif M > 64 and n_splits > 1 and tcgen05_splits(M, N, K) and os.environ.get("LGML_GEMM_PAIR") != "0":
@@ -761,8 +808,8 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
         stages = -(-K // 128)
         n_splits = -(-stages // -(-stages // min(n_splits, stages)))
     n_splits = max(1, min(n_splits, -(-K // 64)))
-    if swiglu and n_splits != 1:
-        raise KernelError("gemm_tcgen05: the gated epilogue takes no K split")
+    if (swiglu or relu_sq) and n_splits != 1:
+        raise KernelError("gemm_tcgen05: an epilogue with an activation takes no K split")
     raw = partials_ok and n_splits > 1
     if n_splits > 1:
         need = n_splits * M * N
@@ -780,7 +827,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
     fn = _fn("gemm_tcgen05", "lgml_gemm_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                    c_int, c_void_p, c_int, c_int, c_void_p, c_void_p])
     _check("gemm_tcgen05", fn(_ptr(x), _ptr(w), _ptr(bias), _ptr(None if raw else out), y_f32, M, N, K, ldx, ldw, ldy,
-                              n_splits, _ptr(scratch if n_splits > 1 else None), 1 if swiglu else 0, 0 if raw else 1, _ptr(status),
+                              n_splits, _ptr(scratch if n_splits > 1 else None), 1 if swiglu else (2 if relu_sq else 0), 0 if raw else 1, _ptr(status),
                               _stream()), "gemm_tcgen05")
     if raw:
         return Partials(scratch[: n_splits * M * N].view(n_splits, M, N), bias)
@@ -829,6 +876,14 @@ def gemm_bf16_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, bias_pairs: Optiona
     if x.shape[0] == 0:
         return out
     return gemm_tcgen05(x, w_pairs, out, bias_pairs, status, swiglu=True)
+
+
+def gemm_bf16_relu_sq(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], status: torch.Tensor) -> torch.Tensor:
+    """act[M, F] = relu(x . w^T + bias)^2 in one kernel (bfloat16 in and out)."""
+    out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.bfloat16, device=x.device)
+    if x.shape[0] == 0:
+        return out
+    return gemm_tcgen05(x, w, out, bias, status, relu_sq=True)
 
 
 _sm_count = None

@@ -85,7 +85,10 @@ class DenseMLP(Part):
         return [self.wu]
 
     def forward(self, rt, h):
-        act = ops.relu_sq(rt.linear(h, self.wu, bias=self.bu))
+        if rt.fused_swiglu(h, self.wu):       # the product's epilogue applies the activation
+            act = ops.gemm_bf16_relu_sq(h, self.wu, self.bu, rt.status)
+        else:
+            act = ops.relu_sq(rt.linear(h, self.wu, bias=self.bu))
         return rt.linear(act, self.wd, bias=self.bd, partials_ok=True)
 
 

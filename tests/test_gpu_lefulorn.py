@@ -44,7 +44,7 @@ def paged(T, G, D, Dv, dtype, seed=0):
     return k, v, table
 
 
-def run_sink_attention(q, k, v, sink, scale, window, dtype, temp=None, gate=None, keep_mode=0, kept=None, lam=None, pos0=0):
+def run_sink_attention(q, k, v, sink, scale, window, dtype, temp=None, gate=None, keep_mode=0, kept=None, lam=None, pos0=0, mma=False):
     """q [T, H, D], k [T, G, D], v [T, G, Dv] (float64) through sink_qkv_store and sink_attention."""
     from lgml_b200 import ops
 
@@ -59,19 +59,25 @@ def run_sink_attention(q, k, v, sink, scale, window, dtype, temp=None, gate=None
                             temp_every=temp[1] if temp else 1, v_mode=keep_mode, v_keep=kept, v_lambda=lam)
     out = torch.empty(T, Hh * Dv, dtype=dtype, device=DEV)
     slopes = P.distance_slopes(Hh).float().to(DEV)
-    ops.sink_attention(qd, positions, seq, table, kp, vp, out, Hh, scale, window or 0, status, slopes=slopes,
-                       sinks=sink.float().to(DEV), gate=gate)
+    if mma:     # the tensor-core form: tiles of at most 64 tokens, here 64, 64, ..., and the rest
+        tiles = torch.tensor([[0, r0, min(64, T - r0), 0] for r0 in range(0, T, 64)], dtype=torch.int32, device=DEV)
+        ops.sink_attention_mma(qd, positions, tiles, table, kp, vp, out, Hh, scale, window or 0, status, slopes=slopes,
+                               sinks=sink.float().to(DEV), gate=gate)
+    else:
+        ops.sink_attention(qd, positions, seq, table, kp, vp, out, Hh, scale, window or 0, status, slopes=slopes,
+                           sinks=sink.float().to(DEV), gate=gate)
     assert int(status.item()) == 0
     return out.double().cpu().view(T, Hh, Dv)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, "mma"])
 @pytest.mark.parametrize("window", [None, 1, 5, 64, 70, 129])
 def test_sink_attention_edges_of_the_window_and_far_keys(dtype, window):
     """Grouped heads, D != Dv, 200 tokens on shuffled pages.  For every query the key at distance
     window - 1 (the last one inside) and the one at distance window (the first one outside) get
     scores far above the rest; without a window, key 3 outweighs the hundreds after it."""
     torch.manual_seed(1)
+    mma, dtype = dtype == "mma", torch.bfloat16 if dtype == "mma" else dtype
     T, Hh, G, D, Dv = 200, 6, 2, 24, 10
     q = torch.randn(T, Hh, D, dtype=F64) * 0.3
     k = torch.randn(T, G, D, dtype=F64) * 0.3
@@ -89,7 +95,7 @@ def test_sink_attention_edges_of_the_window_and_far_keys(dtype, window):
     if dtype == torch.bfloat16:
         q, k, v = (t.to(torch.bfloat16).double() for t in (q, k, v))
     sink = torch.tensor([0.5, -1.0, 2.0, 0.0, 1.0, -0.5], dtype=F64)
-    got = run_sink_attention(q, k, v, sink, 0.7, window, dtype)
+    got = run_sink_attention(q, k, v, sink, 0.7, window, dtype, mma=mma)
     want = P.sink_attention(q, k, v, sink, 0.7, window, P.distance_slopes(Hh))
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     assert float((got - want).abs().max()) < tol, float((got - want).abs().max())
@@ -129,11 +135,16 @@ def test_sink_share_temperature_mixing_and_gate():
     want_mixed = P.sink_attention(q, k, (1 - 0.35) * v2 + 0.35 * v.float().double(), sink, 0.4, None, P.distance_slopes(Hh))
     assert float((mixed - want_mixed).abs().max()) < 2e-5
     assert float((first - P.sink_attention(q, k, v, sink, 0.4, None, P.distance_slopes(Hh))).abs().max()) < 2e-5
+    # the tensor-core form with a start in the middle of a page, the temperature and head sizes that are no multiple of 8
+    got16 = run_sink_attention(q, k, v, sink, 0.4, 50, torch.bfloat16, temp=temp, pos0=pos0, mma=True)
+    assert float((got16 - want).abs().max()) < 3e-2
     # the gate, from a column slice of a wider buffer
     wide = torch.randn(T, Hh * Dv + 7, dtype=torch.float32, device=DEV)
     gated = run_sink_attention(q, k, v, sink, 0.4, None, torch.float32, gate=wide[:, 3:3 + Hh * Dv])
     want_gated = first * torch.sigmoid(wide[:, 3:3 + Hh * Dv].double().cpu()).view(T, Hh, Dv)
     assert float((gated - want_gated).abs().max()) < 2e-5
+    gated16 = run_sink_attention(q, k, v, sink, 0.4, None, torch.bfloat16, gate=wide[:, 3:3 + Hh * Dv], mma=True)
+    assert float((gated16 - want_gated).abs().max()) < 3e-2
 
 
 @pytest.mark.parametrize("D,Dv,Hh,G", [(12, 20, 3, 1), (40, 12, 2, 2), (128, 64, 2, 1), (200, 130, 1, 1)])
