@@ -372,6 +372,313 @@ int launch_mma(dim3 grid, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, 
                 n_pages, slopes, sinks, gate, ldg, out, ldo, H, Hkv, D, Dv, scale, window, status);
     return lgml_launch_status("sink_attention_mma");
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decoding and short portions, bfloat16: every query token on its own, its keys cut into
+// `n_splits` ranges of 32-key blocks.  A CTA takes (token, KV head [x chunk of up to GH of its
+// query heads], range): the query heads that share a KV head are scored together, so each key and
+// value is read once for all of them.  Within a warp the two halves of the work are laid out
+// differently, so that neither needs a reduction across lanes per key: for q . k every lane owns
+// one key of a block of 32 and reads its whole row; for the weighted sum of v every lane owns a few
+// value columns and walks the block's keys, with the weights passed through shared memory.  All
+// loads of a block are independent of each other and go out together.  A range leaves an
+// unnormalised partial result (maximum, sum, weighted values); sink_decode_combine merges the
+// ranges in order, lets the sink join the denominator and applies the gate.
+// ---------------------------------------------------------------------------------------------
+constexpr int DEC_WARPS = 4;
+constexpr int DEC_COLS = 8;        // value columns per lane: two chunks of 4 (VEC), or 8 strided ones
+constexpr int DEC_MAX_SPLITS = 64;
+
+template <int GH, bool VEC>
+__global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_kernel(
+    const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
+    const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
+    const __nv_bfloat16 *__restrict__ v_pages, int n_pages, const float *__restrict__ slopes, const float *__restrict__ sinks,
+    const float *__restrict__ gate, int ldg, __nv_bfloat16 *__restrict__ out, int ldo, float *__restrict__ part_o,
+    float2 *__restrict__ part_ml, int n_splits, int n_chunks, int H, int Hkv, int D, int Dv, float scale, int window,
+    int v_stage, int *__restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float dsm[];
+    float *qs = dsm;                                   // [GH][D]
+    float *ps = qs + GH * D;                           // [WARPS][GH][32]
+    float *mw = ps + DEC_WARPS * GH * 32;              // [WARPS][GH] maxima, then [WARPS][GH] sums
+    float *lw = mw + DEC_WARPS * GH;
+    float *ow = lw + DEC_WARPS * GH;                   // [WARPS][GH][Dv]
+    // [WARPS][32][Dv] bfloat16 when v_stage: a block's values, copied while its scores are computed
+    __nv_bfloat16 *vstage = reinterpret_cast<__nv_bfloat16 *>(ow + DEC_WARPS * GH * Dv) + (size_t)(threadIdx.x >> 5) * 32 * Dv;
+    const int t = blockIdx.x;
+    const int g = blockIdx.y / n_chunks, chunk = blockIdx.y - g * n_chunks;
+    const int split = blockIdx.z;
+    const int group = H / Hkv;
+    const int h0 = g * group + chunk * GH;
+    const int g_count = min(GH, group - chunk * GH);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = positions[t];
+    const int *table = block_table + (size_t)seq_of_token[t] * max_blocks;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const float LOG2E = 1.4426950408889634f;
+    const float scale2 = scale * LOG2E;
+
+    for (int i = threadIdx.x; i < GH * D; i += blockDim.x) {
+        const int hh = i / D, d = i - hh * D;
+        qs[i] = hh < g_count ? __bfloat162float(act_load(q + (size_t)t * ldq + (size_t)(h0 + hh) * D + d)) : 0.f;
+    }
+    __syncthreads();
+    float slope2[GH];
+#pragma unroll
+    for (int hh = 0; hh < GH; ++hh) slope2[hh] = (slopes && hh < g_count) ? slopes[h0 + hh] * LOG2E : 0.f;
+
+    const int b_lo = lo / 32, b_hi = pos / 32;
+    const int per = (b_hi - b_lo + 1 + n_splits - 1) / n_splits;
+    const int b0 = b_lo + split * per, b1 = min(b0 + per, b_hi + 1);
+
+    float m_run[GH], l_run[GH], acc[GH][DEC_COLS];
+#pragma unroll
+    for (int hh = 0; hh < GH; ++hh) {
+        m_run[hh] = -INFINITY;
+        l_run[hh] = 0.f;
+#pragma unroll
+        for (int c = 0; c < DEC_COLS; ++c) acc[hh][c] = 0.f;
+    }
+    float *pw = ps + warp * GH * 32;
+    for (int b = b0 + warp; b < b1; b += DEC_WARPS) {
+        const int pg = b >> 1;
+        const int page = pg < max_blocks ? table[pg] : -1;
+        if (page < 0 || page >= n_pages) {
+            if (lane == 0) atomicExch(status, 3);
+            continue;
+        }
+        const size_t cell0 = ((size_t)page * Hkv + g) * PAGE + (size_t)(b & 1) * 32;     // the block's first cell
+        const int j = b * 32 + lane;
+        const bool ok = j >= lo && j <= pos;
+        const int k_first = max(lo - b * 32, 0), k_last = min(pos - b * 32, 31);
+        const __nv_bfloat16 *vbase = v_pages + cell0 * Dv;
+        if (v_stage) {
+            // the block's visible values on their way into shared memory (through L2) while the scores are computed
+            const int chunks = Dv / 8;
+            for (int c = lane; c < (k_last - k_first + 1) * chunks; c += 32) {
+                const int kk = k_first + c / chunks, d = (c % chunks) * 8;
+                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(vstage + (size_t)kk * Dv + d);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vbase + (size_t)kk * Dv + d) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        float sc[GH];
+#pragma unroll
+        for (int hh = 0; hh < GH; ++hh) sc[hh] = 0.f;
+        if (ok) {
+            const __nv_bfloat16 *krow = k_pages + (cell0 + lane) * D;
+            if (VEC) {
+                // sixteen 16-byte loads (128 elements of the key's row) go out before the first is used
+                for (int c0 = 0; c0 < D; c0 += 128) {
+                    uint4 raw[16];
+#pragma unroll
+                    for (int u = 0; u < 16; ++u)
+                        if (c0 + u * 8 < D) raw[u] = act_load(reinterpret_cast<const uint4 *>(krow + c0 + u * 8));
+#pragma unroll
+                    for (int u = 0; u < 16; ++u) {
+                        const int c = c0 + u * 8;
+                        if (c >= D) break;
+                        const __nv_bfloat162 *pr = reinterpret_cast<const __nv_bfloat162 *>(&raw[u]);
+                        float kf[8];
+#pragma unroll
+                        for (int v2 = 0; v2 < 4; ++v2) {
+                            const float2 f = __bfloat1622float2(pr[v2]);
+                            kf[2 * v2] = f.x;
+                            kf[2 * v2 + 1] = f.y;
+                        }
+#pragma unroll
+                        for (int hh = 0; hh < GH; ++hh) {
+                            const float4 qa = *reinterpret_cast<const float4 *>(qs + hh * D + c), qb = *reinterpret_cast<const float4 *>(qs + hh * D + c + 4);
+                            sc[hh] = fmaf(qa.x, kf[0], fmaf(qa.y, kf[1], fmaf(qa.z, kf[2], fmaf(qa.w, kf[3], sc[hh]))));
+                            sc[hh] = fmaf(qb.x, kf[4], fmaf(qb.y, kf[5], fmaf(qb.z, kf[6], fmaf(qb.w, kf[7], sc[hh]))));
+                        }
+                    }
+                }
+            } else {
+                for (int d = 0; d < D; ++d) {
+                    const float kf = __bfloat162float(act_load(krow + d));
+#pragma unroll
+                    for (int hh = 0; hh < GH; ++hh) sc[hh] = fmaf(qs[hh * D + d], kf, sc[hh]);
+                }
+            }
+        }
+        float corr[GH];
+#pragma unroll
+        for (int hh = 0; hh < GH; ++hh) {
+            const float sv = ok ? sc[hh] * scale2 - slope2[hh] * (float)(pos - j) : -INFINITY;
+            const float m_new = fmaxf(m_run[hh], warp_max(sv));
+            corr[hh] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[hh] - m_new);
+            const float p = (m_new == -INFINITY) ? 0.f : exp2f(sv - m_new);
+            m_run[hh] = m_new;
+            l_run[hh] = l_run[hh] * corr[hh] + p;          // this lane's keys; the lanes are added up at the end
+            pw[hh * 32 + lane] = p;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int hh = 0; hh < GH; ++hh)
+#pragma unroll
+            for (int c = 0; c < DEC_COLS; ++c) acc[hh][c] *= corr[hh];
+        if (v_stage) {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncwarp();
+            for (int kk = k_first; kk <= k_last; ++kk) {
+                float vf[DEC_COLS];
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int d = (lane + 32 * i) * 4;
+                    float2 raw = make_float2(0.f, 0.f);
+                    if (d < Dv) raw = *reinterpret_cast<const float2 *>(vstage + (size_t)kk * Dv + d);
+                    const __nv_bfloat162 *pr = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+                    const float2 f0 = __bfloat1622float2(pr[0]), f1 = __bfloat1622float2(pr[1]);
+                    vf[4 * i] = f0.x, vf[4 * i + 1] = f0.y, vf[4 * i + 2] = f1.x, vf[4 * i + 3] = f1.y;
+                }
+#pragma unroll
+                for (int hh = 0; hh < GH; ++hh) {
+                    const float p = pw[hh * 32 + kk];
+#pragma unroll
+                    for (int c = 0; c < DEC_COLS; ++c) acc[hh][c] = fmaf(p, vf[c], acc[hh][c]);
+                }
+            }
+        } else if (VEC) {
+            // eight keys at a time: their loads go out together
+            for (int kb = k_first; kb <= k_last; kb += 8) {
+                float2 raw[8][2];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int d = (lane + 32 * i) * 4;
+                        raw[u][i] = (kb + u <= k_last && d < Dv) ? act_load(reinterpret_cast<const float2 *>(vbase + (size_t)(kb + u) * Dv + d))
+                                                                 : make_float2(0.f, 0.f);
+                    }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (kb + u > k_last) break;
+                    float vf[DEC_COLS];
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const __nv_bfloat162 *pr = reinterpret_cast<const __nv_bfloat162 *>(&raw[u][i]);
+                        const float2 f0 = __bfloat1622float2(pr[0]), f1 = __bfloat1622float2(pr[1]);
+                        vf[4 * i] = f0.x, vf[4 * i + 1] = f0.y, vf[4 * i + 2] = f1.x, vf[4 * i + 3] = f1.y;
+                    }
+#pragma unroll
+                    for (int hh = 0; hh < GH; ++hh) {
+                        const float p = pw[hh * 32 + kb + u];
+#pragma unroll
+                        for (int c = 0; c < DEC_COLS; ++c) acc[hh][c] = fmaf(p, vf[c], acc[hh][c]);
+                    }
+                }
+            }
+        } else {
+            for (int kk = k_first; kk <= k_last; ++kk) {
+                float vf[DEC_COLS];
+                const __nv_bfloat16 *vrow = vbase + (size_t)kk * Dv;
+#pragma unroll
+                for (int c = 0; c < DEC_COLS; ++c) {
+                    const int d = lane + 32 * c;
+                    vf[c] = d < Dv ? __bfloat162float(act_load(vrow + d)) : 0.f;
+                }
+#pragma unroll
+                for (int hh = 0; hh < GH; ++hh) {
+                    const float p = pw[hh * 32 + kk];
+#pragma unroll
+                    for (int c = 0; c < DEC_COLS; ++c) acc[hh][c] = fmaf(p, vf[c], acc[hh][c]);
+                }
+            }
+        }
+        __syncwarp();
+    }
+    // the four warps' partial results, merged in warp order
+#pragma unroll
+    for (int hh = 0; hh < GH; ++hh) {
+        const float l = warp_sum(l_run[hh]);
+        if (lane == 0) {
+            mw[warp * GH + hh] = m_run[hh];
+            lw[warp * GH + hh] = l;
+        }
+#pragma unroll
+        for (int c = 0; c < DEC_COLS; ++c) {
+            const int d = VEC ? (lane + 32 * (c >> 2)) * 4 + (c & 3) : lane + 32 * c;
+            if (d < Dv) ow[((size_t)warp * GH + hh) * Dv + d] = acc[hh][c];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < g_count * Dv; i += blockDim.x) {
+        const int hh = i / Dv, d = i - hh * Dv;
+        float m = -INFINITY;
+        for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, mw[w * GH + hh]);
+        float o = 0.f, l = 0.f;
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float f = (mw[w * GH + hh] == -INFINITY) ? 0.f : exp2f(mw[w * GH + hh] - m);
+            o += ow[((size_t)w * GH + hh) * Dv + d] * f;
+            l += lw[w * GH + hh] * f;
+        }
+        const int h = h0 + hh;
+        if (n_splits == 1) {
+            const float sink2 = sinks ? sinks[h] * LOG2E : -INFINITY;
+            const float m_all = fmaxf(m, sink2);
+            const float f = (m == -INFINITY) ? 0.f : exp2f(m - m_all);
+            const float den = l * f + (sinks ? exp2f(sink2 - m_all) : 0.f);
+            float r = den > 0.f ? o * f / den : 0.f;
+            if (gate) r *= 1.0f / (1.0f + __expf(-act_load(gate + (size_t)t * ldg + (size_t)h * Dv + d)));
+            out[(size_t)t * ldo + (size_t)h * Dv + d] = __float2bfloat16_rn(r);
+        } else {
+            part_o[(((size_t)t * H + h) * n_splits + split) * Dv + d] = o;
+            if (d == 0) part_ml[((size_t)t * H + h) * n_splits + split] = make_float2(m, l);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128) sink_decode_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__ part_ml,
+                                                                  const float *__restrict__ sinks, const float *__restrict__ gate, int ldg,
+                                                                  __nv_bfloat16 *__restrict__ out, int ldo, int n_splits, int H, int Dv) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float f_s[DEC_MAX_SPLITS];
+    __shared__ float inv_s;
+    const int t = blockIdx.x, h = blockIdx.y;
+    const float2 *ml = part_ml + ((size_t)t * H + h) * n_splits;
+    if (threadIdx.x == 0) {
+        float m = -INFINITY;
+        for (int i = 0; i < n_splits; ++i) m = fmaxf(m, act_load(ml + i).x);
+        const float sink2 = sinks ? sinks[h] * 1.4426950408889634f : -INFINITY;
+        const float m_all = fmaxf(m, sink2);
+        float den = sinks ? exp2f(sink2 - m_all) : 0.f;
+        for (int i = 0; i < n_splits; ++i) {
+            const float2 v = act_load(ml + i);
+            const float f = (v.x == -INFINITY) ? 0.f : exp2f(v.x - m_all);
+            f_s[i] = f;
+            den += v.y * f;
+        }
+        inv_s = den > 0.f ? 1.0f / den : 0.f;
+    }
+    __syncthreads();
+    const float *po = part_o + ((size_t)t * H + h) * n_splits * Dv;
+    for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
+        float o = 0.f;
+        for (int i = 0; i < n_splits; ++i) o += act_load(po + (size_t)i * Dv + d) * f_s[i];
+        o *= inv_s;
+        if (gate) o *= 1.0f / (1.0f + __expf(-act_load(gate + (size_t)t * ldg + (size_t)h * Dv + d)));
+        out[(size_t)t * ldo + (size_t)h * Dv + d] = __float2bfloat16_rn(o);
+    }
+}
+
+template <int GH, bool VEC>
+int launch_decode(dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token,
+                  const int *block_table, int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages,
+                  const float *slopes, const float *sinks, const float *gate, int ldg, __nv_bfloat16 *out, int ldo, float *part_o,
+                  float2 *part_ml, int n_splits, int n_chunks, int H, int Hkv, int D, int Dv, float scale, int window, int v_stage,
+                  int *status) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(sink_decode_kernel<GH, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LGML_FAIL("sink_decode: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    lgml_launch(sink_decode_kernel<GH, VEC>, grid, DEC_WARPS * 32, smem, stream, q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages,
+                v_pages, n_pages, slopes, sinks, gate, ldg, out, ldo, part_o, part_ml, n_splits, n_chunks, H, Hkv, D, Dv, scale, window, v_stage, status);
+    return lgml_launch_status("sink_decode");
+}
 }  // namespace
 
 // proj: float32 [n_tokens, ldp], columns q (H D) | k (Hkv D) | v (Hkv Dv) | anything else.
@@ -458,4 +765,50 @@ LGML_API int lgml_sink_attention_mma(const void *q, int ldq, const int *position
     }
 #undef LGML_MMA_NV
 #undef LGML_MMA_ARGS
+}
+
+// The split form for decoding and short portions (bfloat16, pages of 64, head sizes up to 256).
+// scratch (float32, n_tokens H n_splits (Dv + 2) elements) is needed when n_splits > 1.
+LGML_API int lgml_sink_decode(const void *q, int ldq, const int *positions, const int *seq_of_token, const int *block_table, int max_blocks,
+                              const void *k_pages, const void *v_pages, int n_pages, int page_size, const float *slopes, const float *sinks,
+                              const float *gate, int ldg, void *out, int ldo, float *scratch, int n_splits, int n_tokens, int H, int Hkv,
+                              int D, int Dv, float scale, int window, int *status, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && D > 0 && Dv > 0 && max_blocks > 0, "sink_decode: bad sizes");
+    LGML_REQUIRE(page_size == PAGE, "sink_decode: pages of %d tokens, this kernel takes %d", page_size, PAGE);
+    LGML_REQUIRE(H % Hkv == 0, "sink_decode: %d heads are no multiple of %d KV heads", H, Hkv);
+    LGML_REQUIRE(D <= MAX_D && Dv <= MAX_D, "sink_decode: head sizes %d and %d must be at most %d", D, Dv, MAX_D);
+    LGML_REQUIRE(n_splits >= 1 && n_splits <= DEC_MAX_SPLITS, "sink_decode: %d key ranges (1 to %d)", n_splits, DEC_MAX_SPLITS);
+    LGML_REQUIRE(n_splits == 1 || scratch != nullptr, "sink_decode: %d ranges need scratch memory", n_splits);
+    LGML_REQUIRE(window >= 0, "sink_decode: bad window");
+    LGML_REQUIRE(gate == nullptr || ldg >= H * Dv, "sink_decode: the gate's row stride %d is below H Dv", ldg);
+    if (n_tokens == 0) return 0;
+    const int group = H / Hkv;
+    const int gh = group >= 8 ? 8 : group >= 4 ? 4 : group >= 2 ? 2 : 1;       // heads a CTA scores together
+    const int n_chunks = (group + gh - 1) / gh;
+    LGML_REQUIRE((long long)Hkv * n_chunks <= 65535, "sink_decode: too many heads");
+    const bool vec = D % 8 == 0 && Dv % 4 == 0 && (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
+    // the values of a block go through shared memory when their rows are whole 16-byte pieces (and the floats before them keep that alignment)
+    const int v_stage = vec && Dv % 8 == 0 && D % 4 == 0 && (size_t)DEC_WARPS * 32 * Dv * 2 <= 160 * 1024;
+    const size_t smem = sizeof(float) * ((size_t)gh * D + (size_t)DEC_WARPS * gh * 32 + 2 * DEC_WARPS * gh + (size_t)DEC_WARPS * gh * Dv) +
+                        (v_stage ? (size_t)DEC_WARPS * 32 * Dv * 2 : 0);
+    dim3 grid(n_tokens, Hkv * n_chunks, n_splits);
+    float *part_o = scratch;
+    float2 *part_ml = reinterpret_cast<float2 *>(scratch + (size_t)n_tokens * H * n_splits * Dv);
+    int rc;
+#define LGML_DEC_ARGS grid, smem, stream, (const __nv_bfloat16 *)q, ldq, positions, seq_of_token, block_table, max_blocks, (const __nv_bfloat16 *)k_pages, \
+                      (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, (__nv_bfloat16 *)out, ldo, part_o, part_ml, n_splits, n_chunks, H, \
+                      Hkv, D, Dv, scale, window, v_stage, status
+#define LGML_DEC_GH(G) rc = vec ? launch_decode<G, true>(LGML_DEC_ARGS) : launch_decode<G, false>(LGML_DEC_ARGS); break;
+    switch (gh) {
+        case 8: LGML_DEC_GH(8)
+        case 4: LGML_DEC_GH(4)
+        case 2: LGML_DEC_GH(2)
+        default: LGML_DEC_GH(1)
+    }
+#undef LGML_DEC_GH
+#undef LGML_DEC_ARGS
+    if (rc || n_splits == 1) return rc;
+    lgml_launch(sink_decode_combine_kernel, dim3(n_tokens, H), 128, 0, stream, (const float *)part_o, (const float2 *)part_ml, sinks, gate, ldg,
+                (__nv_bfloat16 *)out, ldo, n_splits, H, Dv);
+    return lgml_launch_status("sink_decode_combine");
 }

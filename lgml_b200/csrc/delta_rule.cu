@@ -13,10 +13,11 @@
 //
 // Four kernels a step:
 //   delta_prepare      one block per token, all tokens at once: convolution (the inputs before a
-//                      portion's first token come from the slot), SiLU, norms, beta, decay
+//                      portion's first token come from the slot), SiLU, norms, beta, decay (beta
+//                      rides behind each head's decays, so the scan copies both as one row)
 //   delta_conv_state   per request: the slot's last taps - 1 inputs after this step
 //   delta_scan         per (request, head, group of value columns): the recurrence over the
-//                      request's tokens in order.  A thread owns rows d = r, r + R, ... of one
+//                      request's tokens in order.  A thread owns a run of consecutive rows of one
 //                      column of S in registers; the R threads of a column add up S^T k and S^T q
 //                      by shuffles in a fixed order.  Columns never talk to each other, so the
 //                      result does not depend on how a prompt was cut or what else is in the batch.
@@ -31,19 +32,19 @@ namespace {
 constexpr int PREP_THREADS = 256;
 constexpr int MAX_TAPS = 16;
 constexpr int SCAN_THREADS = 128;
-constexpr int TCH = 8;            // tokens whose k, q, decay, v and beta a block stages at a time
+constexpr int TCH = 16;           // tokens whose k, q, decay, beta and v a block stages at a time
 
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 // proj columns: q (G D) | k (G D) | v (H Dv) | beta (H) | ...   conv_w: [C, taps], C = 2 G D + H Dv, rows in that order.
 // out_c [tokens, C]: q (unit length, times D^-1/2) | k (unit length) | v, after convolution and SiLU.
+// gb [tokens, H, D + 4]: per head the D decays, beta, and three zeros.
 __global__ void __launch_bounds__(PREP_THREADS) delta_prepare_kernel(
     const float *__restrict__ proj, int ldp, const float *__restrict__ a_pre, int lda, const float *__restrict__ conv_w, int taps,
     const float *__restrict__ state, long long state_stride, long long conv_off, const int *__restrict__ seq_of_token,
     const int *__restrict__ seq_start, const int *__restrict__ slots, const float *__restrict__ a_log,
-    const float *__restrict__ dt_bias, float *__restrict__ out_c, float *__restrict__ beta, float *__restrict__ decay, int H, int G,
-    int D, int Dv) {
+    const float *__restrict__ dt_bias, float *__restrict__ out_c, float *__restrict__ gb, int H, int G, int D, int Dv) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float buf[];             // the token's C channels after convolution and SiLU
@@ -73,10 +74,18 @@ __global__ void __launch_bounds__(PREP_THREADS) delta_prepare_kernel(
         for (int d = lane; d < D; d += 32) dst[hd * D + d] = buf[hd * D + d] * inv;
     }
     for (int c = 2 * G * D + tid; c < C; c += PREP_THREADS) dst[c] = buf[c];
-    for (int h = tid; h < H; h += PREP_THREADS) beta[(size_t)t * H + h] = sigmoid_f(act_load(proj + (size_t)t * ldp + C + h));
-    for (int e = tid; e < H * D; e += PREP_THREADS) {
-        const float rate = expf(a_log[e / D]);
-        decay[(size_t)t * H * D + e] = expf(-rate * softplus_f(act_load(a_pre + (size_t)t * lda + e) + dt_bias[e]));
+    // per head a row of D + 4 floats: the D decays, then beta, then zeros (the row stays a multiple of 16 bytes)
+    const int DB = D + 4;
+    for (int e = tid; e < H * DB; e += PREP_THREADS) {
+        const int h = e / DB, d = e - h * DB;
+        float v = 0.f;
+        if (d < D) {
+            const int c = h * D + d;
+            v = expf(-expf(a_log[h]) * softplus_f(act_load(a_pre + (size_t)t * lda + c) + dt_bias[c]));
+        } else if (d == D) {
+            v = sigmoid_f(act_load(proj + (size_t)t * ldp + C + h));
+        }
+        gb[(size_t)t * H * DB + e] = v;
     }
 }
 
@@ -101,22 +110,35 @@ __global__ void __launch_bounds__(PREP_THREADS) delta_conv_state_kernel(
         }
 }
 
-// NPT rows of one column of S per thread; R threads (a power of two, neighbours in a warp) per column.
-template <int NPT>
+__device__ __forceinline__ void cp_async_16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// NPT consecutive rows (d = r NPT .. r NPT + NPT - 1) of one column of S per thread; R threads (a
+// power of two, neighbours in a warp) per column.  A block stages TCH tokens at a time in shared
+// memory: k, q (thread r's NPT values at floats r (NPT + 4) ..., read as 16-byte pieces; the four
+// floats between two threads' runs keep those reads off each other's banks; rows past D hold 0),
+// the decays laid out alike with beta behind them (decays past D hold 1) and its value columns.  ASYNC (sizes that are multiples of 4 floats): two such buffers, the next chunk copied
+// with cp.async (through L2) while this one is computed; else one buffer filled with plain loads.
+template <int NPT, bool ASYNC>
 __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
-    const float *__restrict__ qkv_c, const float *__restrict__ beta, const float *__restrict__ decay, float *__restrict__ state,
-    long long state_stride, const int *__restrict__ seq_start, const int *__restrict__ slots, float *__restrict__ o_out, int H, int G,
-    int D, int Dv, int R) {
+    const float *__restrict__ qkv_c, const float *__restrict__ gb, float *__restrict__ state, long long state_stride,
+    const int *__restrict__ seq_start, const int *__restrict__ slots, float *__restrict__ o_out, int H, int G, int D, int Dv, int R) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float sm[];
-    const int DP = NPT * R;                               // rows covered (>= D); rows past D hold k = q = 0, decay = 1
+    extern __shared__ __align__(16) float sm[];
+    constexpr int RUN = NPT + 4;                          // floats from one thread's run to the next
+    const int DP = RUN * R;
+    const int DB = D + 4, GP = DP + 4;
     const int cols = SCAN_THREADS / R;
-    float *k_s = sm, *q_s = k_s + TCH * DP, *g_s = q_s + TCH * DP, *v_s = g_s + TCH * DP, *b_s = v_s + TCH * cols;
+    const int buf_floats = TCH * (2 * DP + GP + cols);
     const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int g = h / (H / G);
     const int r = tid % R, col_local = tid / R;
-    const int col = blockIdx.z * cols + col_local;
+    const int col0 = blockIdx.z * cols;
+    const int col = col0 + col_local;
     const bool active = col < Dv;
     const int C = 2 * G * D + H * Dv;
     const int t0 = seq_start[s], n = seq_start[s + 1] - t0;
@@ -125,54 +147,115 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
     float S[NPT];
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
-        const int d = r + R * i;
+        const int d = r * NPT + i;
         S[i] = (active && d < D) ? S_base[(size_t)d * Dv + col] : 0.f;
     }
-    for (int c0 = 0; c0 < n; c0 += TCH) {
+    // what the copies never write: rows past D (a decay of 1 and a key of 0 leave them alone), columns
+    // past Dv; only the token rows and the buffers this launch will use (a decode step has one token)
+    {
+        const int rows = min(n, TCH), nb = (ASYNC && n > TCH) ? 2 : 1;
+        for (int b = 0; b < nb; ++b) {
+            float *k_s = sm + b * buf_floats, *q_s = k_s + TCH * DP, *g_s = q_s + TCH * DP, *v_s = g_s + TCH * GP;
+            for (int e = tid; e < rows * DP; e += SCAN_THREADS) k_s[e] = q_s[e] = 0.f;
+            for (int e = tid; e < rows * GP; e += SCAN_THREADS) g_s[e] = (e % GP) < DP ? 1.f : 0.f;
+            for (int e = tid; e < rows * cols; e += SCAN_THREADS) v_s[e] = 0.f;
+        }
+    }
+    __syncthreads();
+
+    auto stage = [&](int c0, float *buf) {
         const int nt = min(TCH, n - c0);
-        __syncthreads();
-        for (int e = tid; e < nt * DP; e += SCAN_THREADS) {
-            const int i = e / DP, d = e - i * DP;
-            const size_t t = (size_t)(t0 + c0 + i);
-            const bool in = d < D;
-            q_s[e] = in ? act_load(qkv_c + t * C + g * D + d) : 0.f;
-            k_s[e] = in ? act_load(qkv_c + t * C + G * D + g * D + d) : 0.f;
-            g_s[e] = in ? act_load(decay + (t * H + h) * D + d) : 1.f;
+        float *k_s = buf, *q_s = k_s + TCH * DP, *g_s = q_s + TCH * DP, *v_s = g_s + TCH * GP;
+        if (ASYNC) {
+            const int d4 = D / 4, b4 = DB / 4, c4 = cols / 4;
+            for (int e = tid; e < nt * d4; e += SCAN_THREADS) {
+                const int i = e / d4, d = (e - i * d4) * 4;
+                const float *row = qkv_c + (size_t)(t0 + c0 + i) * C + g * D + d;
+                const int at = (d / NPT) * RUN + d % NPT;          // row d in its thread's run
+                cp_async_16(q_s + i * DP + at, row);
+                cp_async_16(k_s + i * DP + at, row + G * D);
+            }
+            for (int e = tid; e < nt * b4; e += SCAN_THREADS) {
+                const int i = e / b4, d = (e - i * b4) * 4;
+                // the decays go to their places, beta (the row's last four floats) behind the padded row
+                cp_async_16(g_s + i * GP + (d < D ? (d / NPT) * RUN + d % NPT : DP), gb + ((size_t)(t0 + c0 + i) * H + h) * DB + d);
+            }
+            for (int e = tid; e < nt * c4; e += SCAN_THREADS) {
+                const int i = e / c4, cl = (e - i * c4) * 4;
+                if (col0 + cl < Dv) cp_async_16(v_s + i * cols + cl, qkv_c + (size_t)(t0 + c0 + i) * C + 2 * G * D + h * Dv + col0 + cl);
+            }
+        } else {
+            for (int e = tid; e < nt * D; e += SCAN_THREADS) {
+                const int i = e / D, d = e - i * D;
+                const float *row = qkv_c + (size_t)(t0 + c0 + i) * C + g * D + d;
+                const int at = (d / NPT) * RUN + d % NPT;
+                q_s[i * DP + at] = act_load(row);
+                k_s[i * DP + at] = act_load(row + G * D);
+            }
+            for (int e = tid; e < nt * (D + 1); e += SCAN_THREADS) {
+                const int i = e / (D + 1), d = e - i * (D + 1);
+                g_s[i * GP + (d < D ? (d / NPT) * RUN + d % NPT : DP)] = act_load(gb + ((size_t)(t0 + c0 + i) * H + h) * DB + d);
+            }
+            for (int e = tid; e < nt * cols; e += SCAN_THREADS) {
+                const int i = e / cols, cl = e - i * cols;
+                if (col0 + cl < Dv) v_s[e] = act_load(qkv_c + (size_t)(t0 + c0 + i) * C + 2 * G * D + h * Dv + col0 + cl);
+            }
         }
-        for (int e = tid; e < nt * cols; e += SCAN_THREADS) {
-            const int i = e / cols, cl = e - i * cols;
-            const int cc = blockIdx.z * cols + cl;
-            v_s[e] = cc < Dv ? act_load(qkv_c + (size_t)(t0 + c0 + i) * C + 2 * G * D + h * Dv + cc) : 0.f;
+    };
+
+    if (ASYNC) {
+        stage(0, sm);
+        cp_async_commit();
+    }
+    int turn = 0;
+    for (int c0 = 0; c0 < n; c0 += TCH, ++turn) {
+        const int nt = min(TCH, n - c0);
+        float *buf = sm + (ASYNC ? (turn & 1) * buf_floats : 0);
+        if (ASYNC) {
+            if (c0 + TCH < n) stage(c0 + TCH, sm + ((turn + 1) & 1) * buf_floats);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            stage(c0, buf);
         }
-        for (int i = tid; i < nt; i += SCAN_THREADS) b_s[i] = act_load(beta + (size_t)(t0 + c0 + i) * H + h);
         __syncthreads();
+        const float *k_s = buf, *q_s = k_s + TCH * DP, *g_s = q_s + TCH * DP, *v_s = g_s + TCH * GP;
         for (int i = 0; i < nt; ++i) {
-            const float *kk = k_s + i * DP + r, *qq = q_s + i * DP + r, *gg = g_s + i * DP + r;
+            // this thread's runs of k, q and the decays, in registers by 16-byte reads
+            float kk[NPT], qq[NPT], gg[NPT];
+#pragma unroll
+            for (int j = 0; j < NPT; j += 4) {
+                *reinterpret_cast<float4 *>(kk + j) = *reinterpret_cast<const float4 *>(k_s + i * DP + r * RUN + j);
+                *reinterpret_cast<float4 *>(gg + j) = *reinterpret_cast<const float4 *>(g_s + i * GP + r * RUN + j);
+                *reinterpret_cast<float4 *>(qq + j) = *reinterpret_cast<const float4 *>(q_s + i * DP + r * RUN + j);
+            }
             // four partial sums each (NPT is a multiple of 4), added in a fixed order: the chain of
             // dependent operations per token is a quarter as long, and the next token waits on it
             float ka[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int j = 0; j < NPT; ++j) {
-                S[j] *= gg[R * j];
-                ka[j & 3] = fmaf(kk[R * j], S[j], ka[j & 3]);
+                S[j] *= gg[j];
+                ka[j & 3] = fmaf(kk[j], S[j], ka[j & 3]);
             }
             float ks = (ka[0] + ka[1]) + (ka[2] + ka[3]);
             for (int o = 1; o < R; o <<= 1) ks += __shfl_xor_sync(0xffffffffu, ks, o);
-            const float u = b_s[i] * (v_s[i * cols + col_local] - ks);
+            const float u = g_s[i * GP + DP] * (v_s[i * cols + col_local] - ks);
             float qa[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int j = 0; j < NPT; ++j) {
-                S[j] = fmaf(kk[R * j], u, S[j]);
-                qa[j & 3] = fmaf(qq[R * j], S[j], qa[j & 3]);
+                S[j] = fmaf(kk[j], u, S[j]);
+                qa[j & 3] = fmaf(qq[j], S[j], qa[j & 3]);
             }
             float oq = (qa[0] + qa[1]) + (qa[2] + qa[3]);
             for (int o = 1; o < R; o <<= 1) oq += __shfl_xor_sync(0xffffffffu, oq, o);
             if (active && r == 0) o_out[(size_t)(t0 + c0 + i) * H * Dv + (size_t)h * Dv + col] = oq;
         }
+        __syncthreads();            // the buffer is free for the copy after next
     }
+    if (ASYNC) cp_async_wait<0>();
 #pragma unroll
     for (int i = 0; i < NPT; ++i) {
-        const int d = r + R * i;
+        const int d = r * NPT + i;
         if (active && d < D) S_base[(size_t)d * Dv + col] = S[i];
     }
 }
@@ -199,19 +282,23 @@ __global__ void __launch_bounds__(128) delta_output_kernel(const float *__restri
     }
 }
 
-template <int NPT>
-int launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const float *qkv_c, const float *beta, const float *decay, float *state,
-                long long state_stride, const int *seq_start, const int *slots, float *o_out, int H, int G, int D, int Dv, int R) {
-    lgml_launch(delta_scan_kernel<NPT>, grid, SCAN_THREADS, smem, stream, qkv_c, beta, decay, state, state_stride, seq_start, slots, o_out, H,
-                G, D, Dv, R);
+template <int NPT, bool ASYNC>
+int launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const float *qkv_c, const float *gb, float *state, long long state_stride,
+                const int *seq_start, const int *slots, float *o_out, int H, int G, int D, int Dv, int R) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<NPT, ASYNC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LGML_FAIL("delta_scan: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    lgml_launch(delta_scan_kernel<NPT, ASYNC>, grid, SCAN_THREADS, smem, stream, qkv_c, gb, state, state_stride, seq_start, slots, o_out, H, G, D,
+                Dv, R);
     return lgml_launch_status("delta_scan");
 }
 }  // namespace
 
 LGML_API int lgml_delta_prepare(const float *proj, int ldp, const float *a_pre, int lda, const float *conv_w, int taps, float *state,
                                 long long state_stride, long long conv_off, const int *seq_of_token, const int *seq_start,
-                                const int *slots, const float *a_log, const float *dt_bias, float *out_c, float *beta, float *decay,
-                                int n_tokens, int n_seqs, int H, int G, int D, int Dv, cudaStream_t stream) {
+                                const int *slots, const float *a_log, const float *dt_bias, float *out_c, float *gb, int n_tokens,
+                                int n_seqs, int H, int G, int D, int Dv, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && n_seqs >= 0 && H > 0 && G > 0 && D > 0 && Dv > 0, "delta_prepare: bad sizes");
     LGML_REQUIRE(H % G == 0, "delta_prepare: %d heads are no multiple of %d key heads", H, G);
     LGML_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "delta_prepare: %d taps (1 to %d)", taps, MAX_TAPS);
@@ -220,7 +307,7 @@ LGML_API int lgml_delta_prepare(const float *proj, int ldp, const float *a_pre, 
     LGML_REQUIRE((size_t)C * sizeof(float) <= 48 * 1024, "delta_prepare: %d channels are more than a block's shared memory holds", C);
     if (n_tokens == 0) return 0;
     lgml_launch(delta_prepare_kernel, dim3(n_tokens), PREP_THREADS, (size_t)C * sizeof(float), stream, proj, ldp, a_pre, lda, conv_w, taps,
-                (const float *)state, state_stride, conv_off, seq_of_token, seq_start, slots, a_log, dt_bias, out_c, beta, decay, H, G, D, Dv);
+                (const float *)state, state_stride, conv_off, seq_of_token, seq_start, slots, a_log, dt_bias, out_c, gb, H, G, D, Dv);
     int rc = lgml_launch_status("delta_prepare");
     if (rc || taps == 1) return rc;
     lgml_launch(delta_conv_state_kernel, dim3(n_seqs, (C + PREP_THREADS - 1) / PREP_THREADS), PREP_THREADS, 0, stream, proj, ldp, taps, state,
@@ -228,27 +315,30 @@ LGML_API int lgml_delta_prepare(const float *proj, int ldp, const float *a_pre, 
     return lgml_launch_status("delta_conv_state");
 }
 
-LGML_API int lgml_delta_scan(const float *qkv_c, const float *beta, const float *decay, float *state, long long state_stride,
-                             const int *seq_start, const int *slots, float *o_out, int n_seqs, int H, int G, int D, int Dv,
-                             cudaStream_t stream) {
+// gb: float32 [tokens, H, D + 4] as delta_prepare writes it (decays, beta, zeros).
+LGML_API int lgml_delta_scan(const float *qkv_c, const float *gb, float *state, long long state_stride, const int *seq_start,
+                             const int *slots, float *o_out, int n_seqs, int H, int G, int D, int Dv, cudaStream_t stream) {
     LGML_REQUIRE(n_seqs >= 0 && H > 0 && G > 0 && D > 0 && Dv > 0 && H % G == 0, "delta_scan: bad sizes");
     LGML_REQUIRE(D <= 1024, "delta_scan: key size %d is over 1024", D);
     LGML_REQUIRE(H <= 65535, "delta_scan: too many heads");
     if (n_seqs == 0) return 0;
     int R = 1;
-    while (R < 32 && (D + R - 1) / R > 32) R *= 2;       // at most 32 rows a thread
+    while (R < 32 && (D + R - 1) / R > 16) R *= 2;       // 16 rows a thread while 32 threads a column suffice
     const int rows = (D + R - 1) / R;
     const int npt = rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
     const int cols = SCAN_THREADS / R;
-    const size_t smem = sizeof(float) * ((size_t)TCH * (3 * (size_t)npt * R + cols) + TCH);
+    const bool async = D % 4 == 0 && Dv % 4 == 0 && (((uintptr_t)qkv_c | (uintptr_t)gb) & 15) == 0;
+    const size_t smem = sizeof(float) * (size_t)(async ? 2 : 1) * TCH * (3 * (size_t)(npt + 4) * R + 4 + cols);
     dim3 grid(n_seqs, H, (Dv + cols - 1) / cols);
-#define LGML_SCAN_ARGS grid, smem, stream, qkv_c, beta, decay, state, state_stride, seq_start, slots, o_out, H, G, D, Dv, R
+#define LGML_SCAN_ARGS grid, smem, stream, qkv_c, gb, state, state_stride, seq_start, slots, o_out, H, G, D, Dv, R
+#define LGML_SCAN_CASE(N) return async ? launch_scan<N, true>(LGML_SCAN_ARGS) : launch_scan<N, false>(LGML_SCAN_ARGS);
     switch (npt) {
-        case 4: return launch_scan<4>(LGML_SCAN_ARGS);
-        case 8: return launch_scan<8>(LGML_SCAN_ARGS);
-        case 16: return launch_scan<16>(LGML_SCAN_ARGS);
-        default: return launch_scan<32>(LGML_SCAN_ARGS);
+        case 4: LGML_SCAN_CASE(4)
+        case 8: LGML_SCAN_CASE(8)
+        case 16: LGML_SCAN_CASE(16)
+        default: LGML_SCAN_CASE(32)
     }
+#undef LGML_SCAN_CASE
 #undef LGML_SCAN_ARGS
 }
 

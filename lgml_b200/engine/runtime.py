@@ -117,6 +117,13 @@ class Runtime:
             tiles = batch.attention_tiles(ops.SINK_TILE_TOKENS)
             return ops.sink_attention_mma(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window,
                                           self.status, slopes=slopes, sinks=sinks, gate=gate)
+        if self.dtype == torch.bfloat16 and self.attention_backend != "ref" and cache.k.shape[2] == 64:
+            # decoding and short portions: every token's keys in ranges, the heads of a KV head together
+            hkv = cache.k.shape[1]
+            reach = min(window, batch.max_kv_len) if window else batch.max_kv_len
+            n_splits = ops.sink_decode_splits(q.shape[0], hkv, n_heads // hkv, reach)
+            return ops.sink_decode(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale, window,
+                                   self.status, n_splits, slopes=slopes, sinks=sinks, gate=gate)
         return ops.sink_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
                                   window, self.status, slopes=slopes, sinks=sinks, gate=gate)
 

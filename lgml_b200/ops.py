@@ -555,6 +555,56 @@ def sink_attention_mma(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Te
     return out
 
 
+def sink_decode_splits(n_tokens: int, n_kv_heads: int, group: int, reach: int) -> int:
+    """Key ranges of the split sink attention: enough CTAs to cover the SMs twice, at least four
+    blocks of 32 keys a range (one per warp), at most 64 ranges.  ``reach``: the most keys a query sees."""
+    gh = 8 if group >= 8 else 4 if group >= 4 else 2 if group >= 2 else 1
+    ctas = max(n_tokens * n_kv_heads * -(-group // gh), 1)
+    blocks = -(-max(reach, 1) // 32) + 1
+    return max(1, min((2 * sm_count()) // ctas, blocks // 4, 64))
+
+
+def sink_decode(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
+                v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int, status: torch.Tensor, n_splits: int,
+                slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``sink_attention`` for decoding and short portions (bfloat16, pages of 64): each token's keys cut into
+    ``n_splits`` ranges, the query heads of a KV head scored together, the ranges merged by a second kernel."""
+    _need(q, "queries", torch.bfloat16, 2)
+    _need(out, "attention output", torch.bfloat16, 2)
+    ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
+    n = q.shape[0]
+    _need(k_pages, "key pages", torch.bfloat16, 4)
+    _need(v_pages, "value pages", torch.bfloat16, 4)
+    n_pages, hkv, page, d = k_pages.shape
+    dv = v_pages.shape[3]
+    _need(positions, "positions", torch.int32, 1)
+    _need(seq_of_token, "request index of tokens", torch.int32, 1)
+    _need(block_table, "block table", torch.int32, 2)
+    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * dv):
+        raise KernelError(f"sink_decode: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {n_heads} heads of {d} and {dv}")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
+        raise KernelError("sink_decode: pages and block table must be contiguous")
+    for t, what in ((slopes, "slopes"), (sinks, "sinks")):
+        if t is not None:
+            _need(t, what, torch.float32, 1)
+            if t.numel() != n_heads or not t.is_contiguous():
+                raise KernelError(f"sink_decode: one of the {what} per head")
+    ldg = 0
+    if gate is not None:
+        _need(gate, "gate", torch.float32, 2)
+        ldg = _rows_contiguous(gate, "gate")
+        if tuple(gate.shape) != (n, n_heads * dv):
+            raise KernelError(f"sink_decode: gate {tuple(gate.shape)} is not [{n}, {n_heads * dv}]")
+    scratch = torch.empty(n * n_heads * n_splits * (dv + 2), dtype=torch.float32, device=q.device) if n_splits > 1 else None
+    fn = _fn("attention_sink", "lgml_sink_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                                    c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                    c_float, c_int, c_void_p, c_void_p])
+    _check("attention_sink", fn(_ptr(q), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(k_pages),
+                                _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), ldo, _ptr(scratch),
+                                int(n_splits), n, n_heads, hkv, d, dv, float(scale), int(window or 0), _ptr(status), _stream()), "sink_decode")
+    return out
+
+
 # ----------------------------------------------------------------------------------------
 # the gated delta rule
 # ----------------------------------------------------------------------------------------
@@ -566,7 +616,8 @@ def delta_prepare(proj: torch.Tensor, a_pre: torch.Tensor, conv_w: torch.Tensor,
     [tokens, q (G D) | k (G D) | v (H Dv) | beta (H) | ...]; ``a_pre`` float32 [tokens, H D];
     ``conv_w`` float32 [2 G D + H Dv, taps]; ``state`` float32 [slots, floats] whose part from
     ``conv_off`` on holds each request's last taps - 1 convolution inputs (updated here).
-    Returns (q | k | v after convolution, SiLU and the norms [tokens, C], beta [tokens, H], decay [tokens, H D])."""
+    Returns (q | k | v after convolution, SiLU and the norms [tokens, C]; per head the D decays, beta and
+    three zeros [tokens, H, D + 4])."""
     _need(proj, "projection output", torch.float32, 2)
     _need(a_pre, "decay input", torch.float32, 2)
     _need(conv_w, "convolution weights", torch.float32, 2)
@@ -586,35 +637,33 @@ def delta_prepare(proj: torch.Tensor, a_pre: torch.Tensor, conv_w: torch.Tensor,
     if seq_of_token.numel() != n or seq_start.numel() != S + 1 or state.shape[1] < conv_off + (taps - 1) * C:
         raise KernelError("delta_prepare: the batch's description or the state's size does not fit")
     out_c = torch.empty((n, C), dtype=torch.float32, device=proj.device)
-    beta = torch.empty((n, n_heads), dtype=torch.float32, device=proj.device)
-    decay = torch.empty((n, n_heads * dim), dtype=torch.float32, device=proj.device)
+    gb = torch.empty((n, n_heads, dim + 4), dtype=torch.float32, device=proj.device)
     fn = _fn("delta_rule", "lgml_delta_prepare", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_void_p,
-                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                   c_int, c_int, c_void_p])
     _check("delta_rule", fn(_ptr(proj), ldp, _ptr(a_pre), lda, _ptr(conv_w), taps, _ptr(state), state.stride(0), int(conv_off), _ptr(seq_of_token),
-                            _ptr(seq_start), _ptr(slots), _ptr(a_log), _ptr(dt_bias), _ptr(out_c), _ptr(beta), _ptr(decay), n, S, n_heads,
+                            _ptr(seq_start), _ptr(slots), _ptr(a_log), _ptr(dt_bias), _ptr(out_c), _ptr(gb), n, S, n_heads,
                             n_kv_heads, dim, vdim, _stream()), "delta_prepare")
-    return out_c, beta, decay
+    return out_c, gb
 
 
-def delta_scan(qkv_c: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, seq_start: torch.Tensor,
-               slots: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, vdim: int) -> torch.Tensor:
+def delta_scan(qkv_c: torch.Tensor, gb: torch.Tensor, state: torch.Tensor, seq_start: torch.Tensor, slots: torch.Tensor,
+               n_heads: int, n_kv_heads: int, dim: int, vdim: int) -> torch.Tensor:
     """The recurrence S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q over each request's
     tokens in order, from and into its slot of ``state`` (S of head h at floats [h D Dv, (h + 1) D Dv)).
-    Returns o float32 [tokens, H Dv]."""
+    ``qkv_c`` [tokens, q | k | v] and ``gb`` [tokens, H, D + 4] (per head the decays, then beta) as
+    ``delta_prepare`` returns them.  Returns o float32 [tokens, H Dv]."""
     n = qkv_c.shape[0]
-    for t, what in ((qkv_c, "prepared q, k, v"), (beta, "beta"), (decay, "decay")):
-        _need(t, what, torch.float32, 2)
-        if not t.is_contiguous() or t.shape[0] != n:
-            raise KernelError(f"delta_scan: {what} must be contiguous with one row per token")
+    _need(qkv_c, "prepared q, k, v", torch.float32, 2)
+    _need(gb, "decays and beta", torch.float32, 3)
     _need(state, "state slots", torch.float32, 2)
-    if qkv_c.shape[1] != 2 * n_kv_heads * dim + n_heads * vdim or beta.shape[1] != n_heads or decay.shape[1] != n_heads * dim \
-            or state.shape[1] < n_heads * dim * vdim or not state.is_contiguous():
+    if qkv_c.shape[1] != 2 * n_kv_heads * dim + n_heads * vdim or tuple(gb.shape) != (n, n_heads, dim + 4) \
+            or state.shape[1] < n_heads * dim * vdim or not (state.is_contiguous() and qkv_c.is_contiguous() and gb.is_contiguous()):
         raise KernelError("delta_scan: shapes disagree")
     o = torch.empty((n, n_heads * vdim), dtype=torch.float32, device=qkv_c.device)
-    fn = _fn("delta_rule", "lgml_delta_scan", [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int,
+    fn = _fn("delta_rule", "lgml_delta_scan", [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                                c_int, c_int, c_int, c_void_p])
-    _check("delta_rule", fn(_ptr(qkv_c), _ptr(beta), _ptr(decay), _ptr(state), state.stride(0), _ptr(seq_start), _ptr(slots), _ptr(o),
+    _check("delta_rule", fn(_ptr(qkv_c), _ptr(gb), _ptr(state), state.stride(0), _ptr(seq_start), _ptr(slots), _ptr(o),
                             slots.numel(), n_heads, n_kv_heads, dim, vdim, _stream()), "delta_scan")
     return o
 

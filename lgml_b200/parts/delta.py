@@ -72,9 +72,9 @@ class ChannelDelta(Part):
         low = rt.linear(h, self.w_low)
         a_pre = rt.linear(low[:, :self.rank_a], self.w_a2, out_dtype=torch.float32)
         g_pre = rt.linear(low[:, self.rank_a:], self.w_g2, out_dtype=torch.float32)
-        qkv_c, beta, decay = ops.delta_prepare(proj, a_pre, self.conv_w, cache.state, self.state_floats, batch.seq_of_token,
-                                               batch.seq_start, batch.slots, self.a_log, self.dt_bias, H, G, D, Dv)
-        o = ops.delta_scan(qkv_c, beta, decay, cache.state, batch.seq_start, batch.slots, H, G, D, Dv)
+        qkv_c, gb = ops.delta_prepare(proj, a_pre, self.conv_w, cache.state, self.state_floats, batch.seq_of_token,
+                                      batch.seq_start, batch.slots, self.a_log, self.dt_bias, H, G, D, Dv)
+        o = ops.delta_scan(qkv_c, gb, cache.state, batch.seq_start, batch.slots, H, G, D, Dv)
         y = ops.delta_output(o, self.norm_w, g_pre, self.eps, rt.dtype, H)
         return rt.linear(y, self.wo, partials_ok=True)
 

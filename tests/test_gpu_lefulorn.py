@@ -59,7 +59,10 @@ def run_sink_attention(q, k, v, sink, scale, window, dtype, temp=None, gate=None
                             temp_every=temp[1] if temp else 1, v_mode=keep_mode, v_keep=kept, v_lambda=lam)
     out = torch.empty(T, Hh * Dv, dtype=dtype, device=DEV)
     slopes = P.distance_slopes(Hh).float().to(DEV)
-    if mma:     # the tensor-core form: tiles of at most 64 tokens, here 64, 64, ..., and the rest
+    if mma == "split":      # the split form for decoding, here on every token of the run
+        ops.sink_decode(qd, positions, seq, table, kp, vp, out, Hh, scale, window or 0, status, 3, slopes=slopes,
+                        sinks=sink.float().to(DEV), gate=gate)
+    elif mma:     # the tensor-core form: tiles of at most 64 tokens, here 64, 64, ..., and the rest
         tiles = torch.tensor([[0, r0, min(64, T - r0), 0] for r0 in range(0, T, 64)], dtype=torch.int32, device=DEV)
         ops.sink_attention_mma(qd, positions, tiles, table, kp, vp, out, Hh, scale, window or 0, status, slopes=slopes,
                                sinks=sink.float().to(DEV), gate=gate)
@@ -70,14 +73,14 @@ def run_sink_attention(q, k, v, sink, scale, window, dtype, temp=None, gate=None
     return out.double().cpu().view(T, Hh, Dv)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, "mma"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, "mma", "split"])
 @pytest.mark.parametrize("window", [None, 1, 5, 64, 70, 129])
 def test_sink_attention_edges_of_the_window_and_far_keys(dtype, window):
     """Grouped heads, D != Dv, 200 tokens on shuffled pages.  For every query the key at distance
     window - 1 (the last one inside) and the one at distance window (the first one outside) get
     scores far above the rest; without a window, key 3 outweighs the hundreds after it."""
     torch.manual_seed(1)
-    mma, dtype = dtype == "mma", torch.bfloat16 if dtype == "mma" else dtype
+    mma, dtype = (dtype if isinstance(dtype, str) else False), (torch.bfloat16 if isinstance(dtype, str) else dtype)
     T, Hh, G, D, Dv = 200, 6, 2, 24, 10
     q = torch.randn(T, Hh, D, dtype=F64) * 0.3
     k = torch.randn(T, G, D, dtype=F64) * 0.3
@@ -145,6 +148,10 @@ def test_sink_share_temperature_mixing_and_gate():
     assert float((gated - want_gated).abs().max()) < 2e-5
     gated16 = run_sink_attention(q, k, v, sink, 0.4, None, torch.bfloat16, gate=wide[:, 3:3 + Hh * Dv], mma=True)
     assert float((gated16 - want_gated).abs().max()) < 3e-2
+    split16 = run_sink_attention(q, k, v, sink, 0.4, None, torch.bfloat16, gate=wide[:, 3:3 + Hh * Dv], mma="split")
+    assert float((split16 - want_gated).abs().max()) < 3e-2
+    got_split = run_sink_attention(q, k, v, sink, 0.4, 50, torch.bfloat16, temp=temp, pos0=pos0, mma="split")
+    assert float((got_split - want).abs().max()) < 3e-2
 
 
 @pytest.mark.parametrize("D,Dv,Hh,G", [(12, 20, 3, 1), (40, 12, 2, 2), (128, 64, 2, 1), (200, 130, 1, 1)])
@@ -183,9 +190,10 @@ def test_delta_scan_in_pieces_matches_the_plain_recurrence(D, Dv, Hh, G):
                 act.append(s)
                 fed[s] += n
             qkv = torch.cat([r[0] for r in rows]).float().to(DEV).contiguous()
-            b = torch.cat([r[1] for r in rows]).float().to(DEV).contiguous()
-            dc = torch.cat([r[2] for r in rows]).float().to(DEV).contiguous()
-            o = ops.delta_scan(qkv, b, dc, state, torch.tensor(starts, dtype=torch.int32, device=DEV), slots[act].contiguous(), Hh, G, D, Dv)
+            b = torch.cat([r[1] for r in rows]).float()
+            dc = torch.cat([r[2] for r in rows]).float().view(-1, Hh, D)
+            gb = torch.cat([dc, b[:, :, None], torch.zeros(b.shape[0], Hh, 3)], 2).to(DEV).contiguous()     # per head: decays, beta, zeros
+            o = ops.delta_scan(qkv, gb, state, torch.tensor(starts, dtype=torch.int32, device=DEV), slots[act].contiguous(), Hh, G, D, Dv)
             for i, s in enumerate(act):
                 outs[s].append(o[starts[i]:starts[i + 1]].cpu())
         assert bool((state[:, Hh * D * Dv:] == 7.0).all()) and bool((state[[1, 3]][:, :Hh * D * Dv] == 0).all())
@@ -226,17 +234,20 @@ def test_delta_prepare_carries_the_filter_inputs_across_portions(taps):
     state = torch.zeros(3, S_floats + (taps - 1) * C, dtype=torch.float32, device=DEV)
     slot = torch.tensor([1], dtype=torch.int32, device=DEV)
     got_c, got_b, got_d = [], [], []
+    tail = []
     fed = 0
     for m in (1, 1, 2, 1, 7, 3, 8):             # portions shorter than the filter among them
         xs = x[fed:fed + m].float().to(DEV).contiguous()
-        c, b, d = ops.delta_prepare(xs, a_pre[fed:fed + m].float().to(DEV).contiguous(), conv_w.float().to(DEV), state, S_floats,
-                                    torch.zeros(m, dtype=torch.int32, device=DEV), torch.tensor([0, m], dtype=torch.int32, device=DEV),
-                                    slot, a_log.float().to(DEV), dt_bias.float().to(DEV), Hh, G, D, Dv)
-        got_c.append(c.cpu()), got_b.append(b.cpu()), got_d.append(d.cpu())
+        c, gb = ops.delta_prepare(xs, a_pre[fed:fed + m].float().to(DEV).contiguous(), conv_w.float().to(DEV), state, S_floats,
+                                  torch.zeros(m, dtype=torch.int32, device=DEV), torch.tensor([0, m], dtype=torch.int32, device=DEV),
+                                  slot, a_log.float().to(DEV), dt_bias.float().to(DEV), Hh, G, D, Dv)
+        gb = gb.cpu()
+        got_c.append(c.cpu()), got_b.append(gb[:, :, D]), got_d.append(gb[:, :, :D].reshape(m, Hh * D)), tail.append(gb[:, :, D + 1:])
         fed += m
     assert fed == n
     for got, want in ((got_c, want_c), (got_b, want_beta), (got_d, want_decay)):
         assert float((torch.cat(got).double() - want).abs().max()) < 1e-5
+    assert bool((torch.cat(tail) == 0).all())
     assert bool((state[[0, 2]] == 0).all()) and bool((state[1, :S_floats] == 0).all())
 
 
