@@ -665,6 +665,236 @@ __global__ void __launch_bounds__(128) sink_decode_combine_kernel(const float *_
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same split, on tensor cores, for head sizes that are multiples of 32 up to 128.  With one
+// query per head the products are turned round: the keys are the M side of the tile and the (up
+// to 8) heads of a KV head the N side:
+//     S^T[64 keys, 8 heads] = K[64, D] . Q^T[D, 8]          O^T[Dv, 8 heads] += V^T[Dv, 64] . P^T[64, 8]
+// Each of the four warps is a pipeline of its own over 16 keys of every page (cp.async, STAGES
+// deep), with a running maximum, sum and output of its own; the four are merged once at the end.
+// The distance bias and the window act on the score fragments; the sink and the gate come in
+// where the result is normalised (here, or in sink_decode_combine when the keys were cut).
+// ---------------------------------------------------------------------------------------------
+constexpr int NH = 8;
+__device__ __forceinline__ void cp_async_16z(void *dst, const void *src, bool valid) {
+    const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+
+template <int KS, int VS, int STAGES>
+__global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_mma_kernel(
+    const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
+    const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
+    const __nv_bfloat16 *__restrict__ v_pages, int n_pages, const float *__restrict__ slopes, const float *__restrict__ sinks,
+    const float *__restrict__ gate, int ldg, __nv_bfloat16 *__restrict__ out, int ldo, float *__restrict__ part_o,
+    float2 *__restrict__ part_ml, int n_splits, int H, int Hkv, int heads_per_cta, int n_chunks, float scale, int window,
+    int *__restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int D = KS * 16, DV = VS * 16;
+    constexpr int LDK = D + 8, LDV = DV + 8;
+    constexpr int WK = PAGE / DEC_WARPS;            // keys of a page per warp: 16
+    constexpr int PW = WK + 8;                      // padded row of a warp's P^T (bfloat16)
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    constexpr size_t WARP_STAGE = (size_t)WK * (LDK + LDV);
+    constexpr size_t WARP_BYTES = (STAGES * WARP_STAGE + NH * PW) * 2;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __nv_bfloat16 *kv_w = reinterpret_cast<__nv_bfloat16 *>(smem_raw + (size_t)warp * WARP_BYTES);
+    __nv_bfloat16 *Pw = kv_w + STAGES * WARP_STAGE;
+
+    const int t = blockIdx.x;
+    const int kvh = blockIdx.y / n_chunks, chunk = blockIdx.y - kvh * n_chunks;
+    const int split = blockIdx.z;
+    const int group = H / Hkv;
+    const int h0 = kvh * group + chunk * heads_per_cta;
+    const int g_count = min(heads_per_cta, group - chunk * heads_per_cta);
+    const int mat = lane >> 3, mrow = lane & 7;
+    const int pos = positions[t];
+    const int *table = block_table + (size_t)seq_of_token[t] * max_blocks;
+    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int n_pages_seq = pos / PAGE + 1;
+    const int first_page = lo / PAGE;
+    const int pps = (n_pages_seq - first_page + n_splits - 1) / n_splits;
+    const int pb = first_page + split * pps;
+    const int pe = min(pb + pps, n_pages_seq);
+    const int n_iter = max(pe - pb, 0);
+    const float LOG2E = 1.4426950408889634f;
+    const float scale2 = scale * LOG2E;
+    // this thread's two heads: columns (lane % 4) * 2 and + 1 of the S^T and O^T fragments
+    float slope2[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        const int head = (lane & 3) * 2 + hh;
+        slope2[hh] = (slopes && head < g_count) ? slopes[h0 + head] * LOG2E : 0.f;
+    }
+
+    auto load_rows = [&](int it) {
+        const int pg = pb + it;
+        const int page = pg < max_blocks ? table[pg] : -1;
+        const bool have = page >= 0 && page < n_pages;
+        if (!have && lane == 0) atomicExch(status, 3);
+        const int valid_rows = have ? min(pos - pg * PAGE + 1, PAGE) : 0;
+        const size_t cell = ((size_t)(have ? page : 0) * Hkv + kvh) * PAGE + (size_t)warp * WK;
+        __nv_bfloat16 *ks_ = kv_w + (size_t)(it % STAGES) * WARP_STAGE, *vs_ = ks_ + WK * LDK;
+#pragma unroll
+        for (int c = lane; c < WK * (D / 8); c += 32) {
+            const int row = c / (D / 8), col = (c - row * (D / 8)) * 8;
+            cp_async_16z(ks_ + row * LDK + col, k_pages + (cell + row) * D + col, warp * WK + row < valid_rows);
+        }
+#pragma unroll
+        for (int c = lane; c < WK * (DV / 8); c += 32) {
+            const int row = c / (DV / 8), col = (c - row * (DV / 8)) * 8;
+            cp_async_16z(vs_ + row * LDV + col, v_pages + (cell + row) * DV + col, warp * WK + row < valid_rows);
+        }
+    };
+#pragma unroll
+    for (int it = 0; it < STAGES - 1; ++it) {
+        if (it < n_iter) load_rows(it);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    // Q^T as B fragments: b0 holds (d = 16 ks + 2 (lane % 4) + {0, 1}, head = lane / 4), b1 the same 8 dims on
+    uint32_t qb[KS][2];
+    {
+        const int head = lane >> 2;
+        const __nv_bfloat16 *qrow = q + (size_t)t * ldq + (size_t)(h0 + head) * D + (lane & 3) * 2;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            qb[ks][0] = head < g_count ? act_load(reinterpret_cast<const unsigned int *>(qrow + ks * 16)) : 0u;
+            qb[ks][1] = head < g_count ? act_load(reinterpret_cast<const unsigned int *>(qrow + ks * 16 + 8)) : 0u;
+        }
+    }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float oacc[VS][4];
+#pragma unroll
+    for (int i = 0; i < VS; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+
+    for (int it = 0; it < n_iter; ++it) {
+        if (it + STAGES - 1 < n_iter) load_rows(it + STAGES - 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");
+        __syncwarp();
+        const int pg = pb + it;
+        const __nv_bfloat16 *ks_ = kv_w + (size_t)(it % STAGES) * WARP_STAGE, *vs_ = ks_ + WK * LDK;
+        const int key_base = pg * PAGE + warp * WK;
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t a[4];
+            ldmatrix_x4(a, ks_ + (size_t)((mat & 1) * 8 + mrow) * LDK + ks * 16 + (mat >> 1) * 8);
+            mma_bf16(c, a, qb[ks][0], qb[ks][1]);
+        }
+        // rows of the fragment are keys (lane / 4, + 8), columns heads ((lane % 4) * 2, + 1)
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int kpos = key_base + (lane >> 2) + (i >> 1) * 8;
+            c[i] = (kpos >= lo && kpos <= pos) ? c[i] * scale2 - slope2[i & 1] * (float)(pos - kpos) : -INFINITY;
+            mx[i & 1] = fmaxf(mx[i & 1], c[i]);
+        }
+        float corr[2];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 4));
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 8));
+            mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 16));
+            const float m_new = fmaxf(m_run[hh], mx[hh]);
+            corr[hh] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[hh] - m_new);
+            m_run[hh] = m_new;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int hh = i & 1;
+            const float pf = (m_run[hh] == -INFINITY) ? 0.f : exp2f(c[i] - m_run[hh]);
+            const __nv_bfloat16 ph = __float2bfloat16_rn(pf);
+            l_run[hh] = (i < 2 ? l_run[hh] * corr[hh] : l_run[hh]) + __bfloat162float(ph);
+            Pw[((lane & 3) * 2 + hh) * PW + (lane >> 2) + (i >> 1) * 8] = ph;
+        }
+        __syncwarp();
+        const uint32_t pb0 = *reinterpret_cast<const uint32_t *>(Pw + (lane >> 2) * PW + (lane & 3) * 2);
+        const uint32_t pb1 = *reinterpret_cast<const uint32_t *>(Pw + (lane >> 2) * PW + (lane & 3) * 2 + 8);
+#pragma unroll
+        for (int mt = 0; mt < VS; ++mt) {
+            oacc[mt][0] *= corr[0];
+            oacc[mt][1] *= corr[1];
+            oacc[mt][2] *= corr[0];
+            oacc[mt][3] *= corr[1];
+            uint32_t a[4];
+            ldmatrix_x4_trans(a, vs_ + (size_t)((mat >> 1) * 8 + mrow) * LDV + mt * 16 + (mat & 1) * 8);
+            mma_bf16(oacc[mt], a, pb0, pb1);
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 4);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 8);
+        l_run[hh] += __shfl_xor_sync(0xffffffffu, l_run[hh], 16);
+    }
+    __syncthreads();                                             // every warp is done with its stages
+    float *mo = reinterpret_cast<float *>(smem_raw);             // [WARPS][DV][NH] outputs, then [WARPS][NH] maxima and sums
+    float *mm = mo + (size_t)DEC_WARPS * DV * NH, *ml = mm + DEC_WARPS * NH;
+#pragma unroll
+    for (int mt = 0; mt < VS; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int d = mt * 16 + (lane >> 2) + (i >> 1) * 8, head = (lane & 3) * 2 + (i & 1);
+            mo[((size_t)warp * DV + d) * NH + head] = oacc[mt][i];
+        }
+    if (lane < 4) {
+        mm[warp * NH + lane * 2] = m_run[0];
+        mm[warp * NH + lane * 2 + 1] = m_run[1];
+        ml[warp * NH + lane * 2] = l_run[0];
+        ml[warp * NH + lane * 2 + 1] = l_run[1];
+    }
+    __syncthreads();
+    for (int i = tid; i < DV * NH; i += DEC_WARPS * 32) {
+        const int d = i / NH, head = i - d * NH;
+        if (head >= g_count) continue;
+        float m = -INFINITY;
+        for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, mm[w * NH + head]);
+        float o = 0.f, l = 0.f;
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float f = (mm[w * NH + head] == -INFINITY) ? 0.f : exp2f(mm[w * NH + head] - m);
+            o += mo[((size_t)w * DV + d) * NH + head] * f;
+            l += ml[w * NH + head] * f;
+        }
+        const int h = h0 + head;
+        if (n_splits == 1) {
+            const float sink2 = sinks ? sinks[h] * LOG2E : -INFINITY;
+            const float m_all = fmaxf(m, sink2);
+            const float f = (m == -INFINITY) ? 0.f : exp2f(m - m_all);
+            const float den = l * f + (sinks ? exp2f(sink2 - m_all) : 0.f);
+            float r = den > 0.f ? o * f / den : 0.f;
+            if (gate) r *= 1.0f / (1.0f + __expf(-act_load(gate + (size_t)t * ldg + (size_t)h * DV + d)));
+            out[(size_t)t * ldo + (size_t)h * DV + d] = __float2bfloat16_rn(r);
+        } else {
+            part_o[(((size_t)t * H + h) * n_splits + split) * DV + d] = o;
+            if (d == 0) part_ml[((size_t)t * H + h) * n_splits + split] = make_float2(m, l);
+        }
+    }
+}
+
+template <int KS, int VS>
+int launch_decode_mma(dim3 grid, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token,
+                      const int *block_table, int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages,
+                      const float *slopes, const float *sinks, const float *gate, int ldg, __nv_bfloat16 *out, int ldo, float *part_o,
+                      float2 *part_ml, int n_splits, int H, int Hkv, int heads_per_cta, int n_chunks, float scale, int window, int *status) {
+    constexpr int STAGES = 3;
+    constexpr int D = KS * 16, DV = VS * 16;
+    const size_t stages = (size_t)DEC_WARPS * ((size_t)STAGES * (PAGE / DEC_WARPS) * (D + 8 + DV + 8) + NH * (PAGE / DEC_WARPS + 8)) * 2;
+    const size_t merge = sizeof(float) * ((size_t)DEC_WARPS * DV * NH + 2 * DEC_WARPS * NH);
+    const size_t smem = stages > merge ? stages : merge;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(sink_decode_mma_kernel<KS, VS, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) LGML_FAIL("sink_decode_mma: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    }
+    lgml_launch(sink_decode_mma_kernel<KS, VS, STAGES>, grid, DEC_WARPS * 32, smem, stream, q, ldq, positions, seq_of_token, block_table, max_blocks,
+                k_pages, v_pages, n_pages, slopes, sinks, gate, ldg, out, ldo, part_o, part_ml, n_splits, H, Hkv, heads_per_cta, n_chunks, scale,
+                window, status);
+    return lgml_launch_status("sink_decode_mma");
+}
+
 template <int GH, bool VEC>
 int launch_decode(dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token,
                   const int *block_table, int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages,
@@ -783,6 +1013,36 @@ LGML_API int lgml_sink_decode(const void *q, int ldq, const int *positions, cons
     LGML_REQUIRE(gate == nullptr || ldg >= H * Dv, "sink_decode: the gate's row stride %d is below H Dv", ldg);
     if (n_tokens == 0) return 0;
     const int group = H / Hkv;
+    float *part_o = scratch;
+    float2 *part_ml = reinterpret_cast<float2 *>(scratch + (size_t)n_tokens * H * n_splits * Dv);
+    if (D % 32 == 0 && Dv % 32 == 0 && D <= 128 && Dv <= 128 && ldq % 2 == 0 && (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0 &&
+        ((uintptr_t)q & 3) == 0) {
+        // head sizes the tensor-core form is built for
+        const int n_chunks = (group + NH - 1) / NH;
+        const int heads_per_cta = (group + n_chunks - 1) / n_chunks;
+        LGML_REQUIRE((long long)Hkv * n_chunks <= 65535, "sink_decode: too many heads");
+        dim3 grid(n_tokens, Hkv * n_chunks, n_splits);
+        int rc = 0;
+#define LGML_DM_ARGS grid, stream, (const __nv_bfloat16 *)q, ldq, positions, seq_of_token, block_table, max_blocks, (const __nv_bfloat16 *)k_pages, \
+                     (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, (__nv_bfloat16 *)out, ldo, part_o, part_ml, n_splits, H, Hkv, \
+                     heads_per_cta, n_chunks, scale, window, status
+#define LGML_DM_VS(KK) \
+    switch (Dv / 16) { case 2: rc = launch_decode_mma<KK, 2>(LGML_DM_ARGS); break; case 4: rc = launch_decode_mma<KK, 4>(LGML_DM_ARGS); break; \
+                       case 6: rc = launch_decode_mma<KK, 6>(LGML_DM_ARGS); break; default: rc = launch_decode_mma<KK, 8>(LGML_DM_ARGS); break; } \
+    break;
+        switch (D / 16) {
+            case 2: LGML_DM_VS(2)
+            case 4: LGML_DM_VS(4)
+            case 6: LGML_DM_VS(6)
+            default: LGML_DM_VS(8)
+        }
+#undef LGML_DM_VS
+#undef LGML_DM_ARGS
+        if (rc || n_splits == 1) return rc;
+        lgml_launch(sink_decode_combine_kernel, dim3(n_tokens, H), 128, 0, stream, (const float *)part_o, (const float2 *)part_ml, sinks, gate, ldg,
+                    (__nv_bfloat16 *)out, ldo, n_splits, H, Dv);
+        return lgml_launch_status("sink_decode_combine");
+    }
     const int gh = group >= 8 ? 8 : group >= 4 ? 4 : group >= 2 ? 2 : 1;       // heads a CTA scores together
     const int n_chunks = (group + gh - 1) / gh;
     LGML_REQUIRE((long long)Hkv * n_chunks <= 65535, "sink_decode: too many heads");
@@ -792,8 +1052,6 @@ LGML_API int lgml_sink_decode(const void *q, int ldq, const int *positions, cons
     const size_t smem = sizeof(float) * ((size_t)gh * D + (size_t)DEC_WARPS * gh * 32 + 2 * DEC_WARPS * gh + (size_t)DEC_WARPS * gh * Dv) +
                         (v_stage ? (size_t)DEC_WARPS * 32 * Dv * 2 : 0);
     dim3 grid(n_tokens, Hkv * n_chunks, n_splits);
-    float *part_o = scratch;
-    float2 *part_ml = reinterpret_cast<float2 *>(scratch + (size_t)n_tokens * H * n_splits * Dv);
     int rc;
 #define LGML_DEC_ARGS grid, smem, stream, (const __nv_bfloat16 *)q, ldq, positions, seq_of_token, block_table, max_blocks, (const __nv_bfloat16 *)k_pages, \
                       (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, (__nv_bfloat16 *)out, ldo, part_o, part_ml, n_splits, n_chunks, H, \

@@ -556,12 +556,13 @@ def sink_attention_mma(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Te
 
 
 def sink_decode_splits(n_tokens: int, n_kv_heads: int, group: int, reach: int) -> int:
-    """Key ranges of the split sink attention: enough CTAs to cover the SMs twice, at least four
-    blocks of 32 keys a range (one per warp), at most 64 ranges.  ``reach``: the most keys a query sees."""
-    gh = 8 if group >= 8 else 4 if group >= 4 else 2 if group >= 2 else 1
-    ctas = max(n_tokens * n_kv_heads * -(-group // gh), 1)
-    blocks = -(-max(reach, 1) // 32) + 1
-    return max(1, min((2 * sm_count()) // ctas, blocks // 4, 64))
+    """Key ranges of the split sink attention: enough CTAs to cover the SMs twice, at least two pages
+    a range, at most 64 ranges, and none of them empty.  ``reach``: the most keys a query sees."""
+    ctas = max(n_tokens * n_kv_heads * -(-group // 8), 1)
+    pages = max(reach, 1) // 64 + 2          # a window of w keys can touch w / 64 + 2 pages
+    want = max(1, min((2 * sm_count()) // ctas, pages // 2, 64))
+    per = -(-pages // want)
+    return -(-pages // per)
 
 
 def sink_decode(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,

@@ -75,13 +75,14 @@ def run_sink_attention(q, k, v, sink, scale, window, dtype, temp=None, gate=None
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, "mma", "split"])
 @pytest.mark.parametrize("window", [None, 1, 5, 64, 70, 129])
-def test_sink_attention_edges_of_the_window_and_far_keys(dtype, window):
+@pytest.mark.parametrize("sizes", [(24, 10), (64, 32)])
+def test_sink_attention_edges_of_the_window_and_far_keys(dtype, window, sizes):
     """Grouped heads, D != Dv, 200 tokens on shuffled pages.  For every query the key at distance
     window - 1 (the last one inside) and the one at distance window (the first one outside) get
     scores far above the rest; without a window, key 3 outweighs the hundreds after it."""
     torch.manual_seed(1)
     mma, dtype = (dtype if isinstance(dtype, str) else False), (torch.bfloat16 if isinstance(dtype, str) else dtype)
-    T, Hh, G, D, Dv = 200, 6, 2, 24, 10
+    T, Hh, G, (D, Dv) = 200, 6, 2, sizes        # (64, 32): sizes the tensor-core decode form takes; (24, 10): its plain twin
     q = torch.randn(T, Hh, D, dtype=F64) * 0.3
     k = torch.randn(T, G, D, dtype=F64) * 0.3
     v = torch.randn(T, G, Dv, dtype=F64)
