@@ -1,6 +1,7 @@
 """lgml_b200: a small, whole inference engine for one B200, after mischief/lgml.
 
-Token ids in, next tokens out, for the Llama dense decoder: typed configuration and
+Token ids in, next tokens out, for the Llama dense decoder and the Lefulorn design (attention
+with a window, a distance bias and a sink beside a gated delta rule): typed configuration and
 an architecture registry, safetensors weights by name, layers assembled from parts, a
 paged cache with block tables, one step function over mixed batches, a scheduler,
 mischief/lgml's sampler, and hand-written sm_100a kernels with a true 32-bit twin.

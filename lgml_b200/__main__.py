@@ -16,7 +16,7 @@ import tempfile
 
 
 def main(argv=None) -> int:
-    ap = argparse.ArgumentParser(prog="lgml_b200", description="generate token ids with the B200 Llama engine")
+    ap = argparse.ArgumentParser(prog="lgml_b200", description="generate token ids with the B200 engine (the architecture is the model folder's)")
     ap.add_argument("-m", "--model", help="model folder (config.json + model.safetensors)")
     ap.add_argument("--random-config", help="a config.json to run with random weights instead of a model folder")
     ap.add_argument("--write-random", metavar="DIR", help="with --random-config: write the random model folder to DIR and exit")

@@ -218,7 +218,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(smem_raw);
     __nv_bfloat16 *Ks = Qs + TILE_Q * LDK;
-    __nv_bfloat16 *Vs = Ks + PAGE * LDK;
+    __nv_bfloat16 *Vs = Ks + 2 * PAGE * LDK;          // two buffers of keys, then two of values
     const int tile = blockIdx.x, h = blockIdx.y;
     const int g = h / (H / Hkv);
     const int seq = tiles[tile * 4], row0 = tiles[tile * 4 + 1], n_tok = tiles[tile * 4 + 2];
@@ -229,7 +229,6 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(
     const int lo_key = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
     const int *table = block_table + (size_t)seq * max_blocks;
     const bool vec_k = (D % 8 == 0) && (ldq % 8 == 0) && ((reinterpret_cast<uintptr_t>(q) & 15) == 0);
-    const bool vec_v = (Dv % 8 == 0);
     const float LOG2E = 1.4426950408889634f;
     const float slope2 = (slopes ? slopes[h] : 0.f) * LOG2E, scale2 = scale * LOG2E;
 
@@ -248,14 +247,49 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(
 #pragma unroll
     for (int i = 0; i < NV; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
 
-    for (int pg = lo_key / PAGE; pg <= p_last / PAGE; ++pg) {
+    // With rows of whole 16-byte pieces the pages come by cp.async into two buffers in turn: the
+    // copy of the next page runs under the products of this one.  Else one buffer, plain loads.
+    const bool pipelined = (D % 8 == 0) && (Dv % 8 == 0);
+    const int pg_first = lo_key / PAGE, pg_last = p_last / PAGE;
+    auto issue = [&](int pg, int buf) {
         const int page = pg < max_blocks ? table[pg] : -1;
         const bool have = page >= 0 && page < n_pages;
         if (!have && threadIdx.x == 0) atomicExch(status, 3);
-        __syncthreads();            // everyone is done with the page before
         const size_t cell0 = ((size_t)(have ? page : 0) * Hkv + g) * PAGE;
-        load_rows(Ks, LDK, PAGE, D, DP, vec_k && (D % 8 == 0), [&](int r) { return have ? k_pages + (cell0 + r) * D : nullptr; });
-        load_rows(Vs, LDV, PAGE, Dv, DVP, vec_v, [&](int r) { return have ? v_pages + (cell0 + r) * Dv : nullptr; });
+        __nv_bfloat16 *Kb = Ks + (size_t)buf * PAGE * LDK, *Vb = Vs + (size_t)buf * PAGE * LDV;
+        for (int c = threadIdx.x; c < PAGE * (DP / 8); c += blockDim.x) {
+            const int r = c / (DP / 8), col = (c - r * (DP / 8)) * 8;
+            const int bytes = (have && col < D) ? 16 : 0;       // 0: zeros
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(Kb + (size_t)r * LDK + col)),
+                         "l"(k_pages + (cell0 + r) * D + (col < D ? col : 0)), "r"(bytes) : "memory");
+        }
+        for (int c = threadIdx.x; c < PAGE * (DVP / 8); c += blockDim.x) {
+            const int r = c / (DVP / 8), col = (c - r * (DVP / 8)) * 8;
+            const int bytes = (have && col < Dv) ? 16 : 0;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(Vb + (size_t)r * LDV + col)),
+                         "l"(v_pages + (cell0 + r) * Dv + (col < Dv ? col : 0)), "r"(bytes) : "memory");
+        }
+    };
+    if (pipelined) {
+        issue(pg_first, 0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (int pg = pg_first; pg <= pg_last; ++pg) {
+        const int buf = pipelined ? ((pg - pg_first) & 1) : 0;
+        const __nv_bfloat16 *Kb = Ks + (size_t)buf * PAGE * LDK, *Vb = Vs + (size_t)buf * PAGE * LDV;
+        __syncthreads();            // everyone is done with the page before: its buffer is free
+        if (pipelined) {
+            if (pg < pg_last) issue(pg + 1, buf ^ 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            const int page = pg < max_blocks ? table[pg] : -1;
+            const bool have = page >= 0 && page < n_pages;
+            if (!have && threadIdx.x == 0) atomicExch(status, 3);
+            const size_t cell0 = ((size_t)(have ? page : 0) * Hkv + g) * PAGE;
+            load_rows(Ks, LDK, PAGE, D, DP, false, [&](int r) { return have ? k_pages + (cell0 + r) * D : nullptr; });
+            load_rows(Vs, LDV, PAGE, Dv, DVP, false, [&](int r) { return have ? v_pages + (cell0 + r) * Dv : nullptr; });
+        }
         __syncthreads();
         // the warp's rows see keys up to their own positions: skip a page that lies wholly outside
         const int w_first = p0 + warp * 16, w_last = min(w_first + 15, p_last);
@@ -270,7 +304,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(
 #pragma unroll
             for (int np = 0; np < 4; ++np) {       // two key tiles of 8 per ldmatrix
                 uint32_t b[4];
-                ldmatrix_x4(b, Ks + (size_t)(np * 16 + (mat >> 1) * 8 + mrow) * LDK + ks * 16 + (mat & 1) * 8);
+                ldmatrix_x4(b, Kb + (size_t)(np * 16 + (mat >> 1) * 8 + mrow) * LDK + ks * 16 + (mat & 1) * 8);
                 mma_bf16(sacc[2 * np], qf[ks], b[0], b[1]);
                 mma_bf16(sacc[2 * np + 1], qf[ks], b[2], b[3]);
             }
@@ -328,7 +362,7 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(
 #pragma unroll
             for (int np = 0; np < NV / 2; ++np) {   // two value tiles of 8 per ldmatrix
                 uint32_t b[4];
-                ldmatrix_x4_trans(b, Vs + (size_t)(kk * 16 + (mat & 1) * 8 + mrow) * LDV + np * 16 + (mat >> 1) * 8);
+                ldmatrix_x4_trans(b, Vb + (size_t)(kk * 16 + (mat & 1) * 8 + mrow) * LDV + np * 16 + (mat >> 1) * 8);
                 mma_bf16(oacc[2 * np], pf[kk], b[0], b[1]);
                 mma_bf16(oacc[2 * np + 1], pf[kk], b[2], b[3]);
             }
@@ -363,7 +397,7 @@ template <int KS, int NV>
 int launch_mma(dim3 grid, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, const int *positions, const int *tiles, const int *block_table,
                int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, const float *slopes, const float *sinks,
                const float *gate, int ldg, __nv_bfloat16 *out, int ldo, int H, int Hkv, int D, int Dv, float scale, int window, int *status) {
-    const size_t smem = ((size_t)(TILE_Q + PAGE) * (KS * 16 + 8) + (size_t)PAGE * (NV * 8 + 8)) * 2;
+    const size_t smem = ((size_t)(TILE_Q + 2 * PAGE) * (KS * 16 + 8) + (size_t)2 * PAGE * (NV * 8 + 8)) * 2;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(sink_attention_mma_kernel<KS, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LGML_FAIL("sink_attention_mma: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
