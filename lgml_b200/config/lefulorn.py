@@ -72,8 +72,16 @@ class LefulornConfig(ModelConfig):
             raise ConfigError("config.json: 'norm' must be an object with 'eps'")
         if not isinstance(d["layers"], list):
             raise ConfigError("config.json: 'layers' must be a list")
+        layers = copy.deepcopy(d["layers"])
+        for layer in layers:        # sizes a mixer may leave out: KV heads default to the heads, values to the keys' size
+            m = layer.get("mixer") if isinstance(layer, dict) else None
+            if isinstance(m, dict):
+                if "heads" in m:
+                    m.setdefault("kv_heads", m["heads"])
+                if "dim" in m:
+                    m.setdefault("vdim", m["dim"])
         return cls(vocab=int(d["vocab"]), width=int(d["width"]), norm_eps=float(norm["eps"]),
-                   logit_scale=float(d.get("logit_scale", 1.0)), layers=copy.deepcopy(d["layers"]),
+                   logit_scale=float(d.get("logit_scale", 1.0)), layers=layers,
                    torch_dtype=str(d.get("torch_dtype", "bfloat16")))
 
     def validate(self) -> None:

@@ -54,7 +54,16 @@ ODD_RANKS = {1: (6, 6), 3: (10, 2)}
 ONLY_DELTA = config(50, 32, [delta(2, 1, 16, 16, conv=4, ff=40), delta(2, 2, 8, 16, conv=4)], eps=1e-6, logit_scale=2.0)
 ONLY_DELTA_RANKS = {0: (8, 8), 1: (8, 8)}
 
-CONFIGS = {"mixed": (MIXED, MIXED_RANKS), "odd": (ODD, ODD_RANKS), "only_delta": (ONLY_DELTA, ONLY_DELTA_RANKS)}
+# Attention only, no window anywhere and no state: the engine then replays short portions from
+# captured steps (padded to a page's edge) and pads decode batches with repeated rows.
+ONLY_ATTENTION = config(83, 48, [
+    attention(4, 2, 16, 8, scale=0.3, v_mix=True, q_temp=(0.4, 3), ff=64),
+    attention(2, 2, 32, 16, scale=0.2),
+    attention(4, 2, 16, 8, scale=0.3, v_mix=True, ff=24),
+], eps=1e-5, logit_scale=1.0)
+
+CONFIGS = {"mixed": (MIXED, MIXED_RANKS), "odd": (ODD, ODD_RANKS), "only_delta": (ONLY_DELTA, ONLY_DELTA_RANKS),
+           "only_attention": (ONLY_ATTENTION, {})}
 
 
 def random_weights(cfg: dict, ranks: Dict[int, Tuple[int, int]], seed: int, sharpen: float = 1.0) -> Dict[str, torch.Tensor]:

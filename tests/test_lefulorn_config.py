@@ -58,6 +58,14 @@ def test_loader_names_what_does_not_fit(tmp_path):
     assert [n for n, _, _ in e.value.wrong_shape] == ["l1.mix.A_log"]
 
 
+def test_sizes_a_mixer_leaves_out():
+    d = json.loads(json.dumps(L.ONLY_ATTENTION))
+    del d["layers"][1]["mixer"]["kv_heads"], d["layers"][1]["mixer"]["vdim"], d["logit_scale"]
+    cfg = config_from_dict(d)
+    att = build_model(cfg).blocks[1].mixer
+    assert (att.n_kv_heads, att.v_head_dim) == (2, 32) and build_model(cfg).logit_scale is None
+
+
 def test_config_errors_name_the_key():
     def broken(edit):
         d = json.loads(json.dumps(L.MIXED))
