@@ -176,6 +176,13 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x by the hardware's approximation (two units in the last place; -inf gives 0): the weights
+// it makes are rounded to bfloat16 for the second product
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&v);
@@ -309,28 +316,45 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(
                 mma_bf16(sacc[2 * np + 1], qf[ks], b[2], b[3]);
             }
         }
-        // scale, distance bias, mask; scores in the base-2 domain
+        // scale, distance bias, mask; scores in the base-2 domain.  Most pages lie wholly inside the
+        // window and before the warp's first row: there every key counts, and the bias of element
+        // (row, key) is a row term plus a key term, one multiply-add and one add a score.
         float mx[2] = {-INFINITY, -INFINITY};
+        const bool interior = key0 + PAGE - 1 <= w_first && (window == 0 || w_last - key0 < window);
+        if (interior) {
+            const float rowt[2] = {-slope2 * (float)(qpos[0] - key0), -slope2 * (float)(qpos[1] - key0)};
+            const float colb = slope2 * (float)((lane & 3) * 2);
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+            for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int rr = i >> 1;
-                const int j = key0 + nt * 8 + (lane & 3) * 2 + (i & 1);
-                const int dist = qpos[rr] - j;
-                const bool ok = qok[rr] && dist >= 0 && (window == 0 || dist < window);
-                const float sv = ok ? sacc[nt][i] * scale2 - slope2 * (float)dist : -INFINITY;
-                sacc[nt][i] = sv;
-                mx[rr] = fmaxf(mx[rr], sv);
-            }
-        float corr[2];
+                for (int i = 0; i < 4; ++i) {
+                    const float sv = fmaf(sacc[nt][i], scale2, rowt[i >> 1] + fmaf(slope2, (float)(nt * 8 + (i & 1)), colb));
+                    sacc[nt][i] = sv;
+                    mx[i >> 1] = fmaxf(mx[i >> 1], sv);
+                }
+        } else {
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int rr = i >> 1;
+                    const int j = key0 + nt * 8 + (lane & 3) * 2 + (i & 1);
+                    const int dist = qpos[rr] - j;
+                    const bool ok = qok[rr] && dist >= 0 && (window == 0 || dist < window);
+                    const float sv = ok ? sacc[nt][i] * scale2 - slope2 * (float)dist : -INFINITY;
+                    sacc[nt][i] = sv;
+                    mx[rr] = fmaxf(mx[rr], sv);
+                }
+        }
+        float corr[2], m_use[2];
 #pragma unroll
         for (int rr = 0; rr < 2; ++rr) {
             mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
             mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
             const float m_new = fmaxf(m_run[rr], mx[rr]);
-            corr[rr] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[rr] - m_new);
+            corr[rr] = (m_new == -INFINITY) ? 1.f : fast_exp2(m_run[rr] - m_new);
             m_run[rr] = m_new;
+            m_use[rr] = (m_new == -INFINITY) ? 0.f : m_new;       // a row that has seen no key yet: every weight is exp2(-inf) = 0
             l_run[rr] *= corr[rr];
         }
         uint32_t pf[4][4];           // P as A fragments: key step kk covers key tiles 2 kk and 2 kk + 1
@@ -338,17 +362,11 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(
         for (int nt = 0; nt < 8; ++nt) {
             float pv[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int rr = i >> 1;
-                pv[i] = (m_run[rr] == -INFINITY) ? 0.f : exp2f(sacc[nt][i] - m_run[rr]);
-            }
-            const uint32_t lo = pack_bf16(pv[0], pv[1]), hi = pack_bf16(pv[2], pv[3]);
-            // the sums run over the weights as the product sees them (rounded to bfloat16)
-            const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162 *>(&lo), hi2 = *reinterpret_cast<const __nv_bfloat162 *>(&hi);
-            l_run[0] += __bfloat162float(lo2.x) + __bfloat162float(lo2.y);
-            l_run[1] += __bfloat162float(hi2.x) + __bfloat162float(hi2.y);
-            pf[nt >> 1][(nt & 1) * 2] = lo;
-            pf[nt >> 1][(nt & 1) * 2 + 1] = hi;
+            for (int i = 0; i < 4; ++i) pv[i] = fast_exp2(sacc[nt][i] - m_use[i >> 1]);
+            l_run[0] += pv[0] + pv[1];
+            l_run[1] += pv[2] + pv[3];
+            pf[nt >> 1][(nt & 1) * 2] = pack_bf16(pv[0], pv[1]);
+            pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(pv[2], pv[3]);
         }
 #pragma unroll
         for (int nv = 0; nv < NV; ++nv) {
