@@ -212,7 +212,7 @@ __device__ __forceinline__ void load_rows(__nv_bfloat16 *dst, int lds, int rows,
 }
 
 template <int KS, int NV>
-__global__ void __launch_bounds__(128) sink_attention_mma_kernel(
+__global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
     const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ tiles,
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, const float *__restrict__ slopes, const float *__restrict__ sinks,
@@ -223,9 +223,11 @@ __global__ void __launch_bounds__(128) sink_attention_mma_kernel(
     constexpr int DP = KS * 16, DVP = NV * 8;
     constexpr int LDK = DP + 8, LDV = DVP + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    __nv_bfloat16 *Qs = reinterpret_cast<__nv_bfloat16 *>(smem_raw);
-    __nv_bfloat16 *Ks = Qs + TILE_Q * LDK;
-    __nv_bfloat16 *Vs = Ks + 2 * PAGE * LDK;          // two buffers of keys, then two of values
+    // two buffers of keys, then two of values; the queries lie in the second buffer of keys until
+    // their fragments are in registers (that buffer is first written for the second page)
+    __nv_bfloat16 *Ks = reinterpret_cast<__nv_bfloat16 *>(smem_raw);
+    __nv_bfloat16 *Qs = Ks + PAGE * LDK;
+    __nv_bfloat16 *Vs = Ks + 2 * PAGE * LDK;
     const int tile = blockIdx.x, h = blockIdx.y;
     const int g = h / (H / Hkv);
     const int seq = tiles[tile * 4], row0 = tiles[tile * 4 + 1], n_tok = tiles[tile * 4 + 2];
@@ -415,7 +417,7 @@ template <int KS, int NV>
 int launch_mma(dim3 grid, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, const int *positions, const int *tiles, const int *block_table,
                int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, const float *slopes, const float *sinks,
                const float *gate, int ldg, __nv_bfloat16 *out, int ldo, int H, int Hkv, int D, int Dv, float scale, int window, int *status) {
-    const size_t smem = ((size_t)(TILE_Q + 2 * PAGE) * (KS * 16 + 8) + (size_t)2 * PAGE * (NV * 8 + 8)) * 2;
+    const size_t smem = ((size_t)2 * PAGE * (KS * 16 + 8) + (size_t)2 * PAGE * (NV * 8 + 8)) * 2;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(sink_attention_mma_kernel<KS, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LGML_FAIL("sink_attention_mma: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
