@@ -122,7 +122,9 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 // floats between two threads' runs keep those reads off each other's banks; rows past D hold 0),
 // the decays laid out alike with beta behind them (decays past D hold 1) and its value columns.  ASYNC (sizes that are multiples of 4 floats): two such buffers, the next chunk copied
 // with cp.async (through L2) while this one is computed; else one buffer filled with plain loads.
-template <int NPT, bool ASYNC>
+// NC columns a thread (column c of a thread lies SCAN_THREADS / R columns after its column c - 1):
+// two independent chains per thread fill the waits of each other, and k, q and the decays are read once for both.
+template <int NPT, bool ASYNC, int NC>
 __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
     const float *__restrict__ qkv_c, const float *__restrict__ gb, float *__restrict__ state, long long state_stride,
     const int *__restrict__ seq_start, const int *__restrict__ slots, float *__restrict__ o_out, int H, int G, int D, int Dv, int R) {
@@ -132,24 +134,25 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
     constexpr int RUN = NPT + 4;                          // floats from one thread's run to the next
     const int DP = RUN * R;
     const int DB = D + 4, GP = DP + 4;
-    const int cols = SCAN_THREADS / R;
+    const int tcols = SCAN_THREADS / R;                   // columns side by side in a block; a thread's columns lie tcols apart
+    const int cols = NC * tcols;
     const int buf_floats = TCH * (2 * DP + GP + cols);
     const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int g = h / (H / G);
     const int r = tid % R, col_local = tid / R;
     const int col0 = blockIdx.z * cols;
-    const int col = col0 + col_local;
-    const bool active = col < Dv;
     const int C = 2 * G * D + H * Dv;
     const int t0 = seq_start[s], n = seq_start[s + 1] - t0;
     float *S_base = state + (size_t)slots[s] * state_stride + (size_t)h * D * Dv;
 
-    float S[NPT];
+    float S[NC][NPT];
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-        const int d = r * NPT + i;
-        S[i] = (active && d < D) ? S_base[(size_t)d * Dv + col] : 0.f;
-    }
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+            const int d = r * NPT + i, col = col0 + col_local + c * tcols;
+            S[c][i] = (col < Dv && d < D) ? S_base[(size_t)d * Dv + col] : 0.f;
+        }
     // what the copies never write: rows past D (a decay of 1 and a key of 0 leave them alone), columns
     // past Dv; only the token rows and the buffers this launch will use (a decode step has one token)
     {
@@ -231,33 +234,53 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
             }
             // four partial sums each (NPT is a multiple of 4), added in a fixed order: the chain of
             // dependent operations per token is a quarter as long, and the next token waits on it
-            float ka[4] = {0.f, 0.f, 0.f, 0.f};
+            float ks[NC], oq[NC];
 #pragma unroll
-            for (int j = 0; j < NPT; ++j) {
-                S[j] *= gg[j];
-                ka[j & 3] = fmaf(kk[j], S[j], ka[j & 3]);
-            }
-            float ks = (ka[0] + ka[1]) + (ka[2] + ka[3]);
-            for (int o = 1; o < R; o <<= 1) ks += __shfl_xor_sync(0xffffffffu, ks, o);
-            const float u = g_s[i * GP + DP] * (v_s[i * cols + col_local] - ks);
-            float qa[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int c = 0; c < NC; ++c) {
+                float ka[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int j = 0; j < NPT; ++j) {
-                S[j] = fmaf(kk[j], u, S[j]);
-                qa[j & 3] = fmaf(qq[j], S[j], qa[j & 3]);
+                for (int j = 0; j < NPT; ++j) {
+                    S[c][j] *= gg[j];
+                    ka[j & 3] = fmaf(kk[j], S[c][j], ka[j & 3]);
+                }
+                ks[c] = (ka[0] + ka[1]) + (ka[2] + ka[3]);
             }
-            float oq = (qa[0] + qa[1]) + (qa[2] + qa[3]);
-            for (int o = 1; o < R; o <<= 1) oq += __shfl_xor_sync(0xffffffffu, oq, o);
-            if (active && r == 0) o_out[(size_t)(t0 + c0 + i) * H * Dv + (size_t)h * Dv + col] = oq;
+            for (int o = 1; o < R; o <<= 1)
+#pragma unroll
+                for (int c = 0; c < NC; ++c) ks[c] += __shfl_xor_sync(0xffffffffu, ks[c], o);
+            const float beta = g_s[i * GP + DP];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const float u = beta * (v_s[i * cols + col_local + c * tcols] - ks[c]);
+                float qa[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int j = 0; j < NPT; ++j) {
+                    S[c][j] = fmaf(kk[j], u, S[c][j]);
+                    qa[j & 3] = fmaf(qq[j], S[c][j], qa[j & 3]);
+                }
+                oq[c] = (qa[0] + qa[1]) + (qa[2] + qa[3]);
+            }
+            for (int o = 1; o < R; o <<= 1)
+#pragma unroll
+                for (int c = 0; c < NC; ++c) oq[c] += __shfl_xor_sync(0xffffffffu, oq[c], o);
+            if (r == 0) {
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    const int col = col0 + col_local + c * tcols;
+                    if (col < Dv) o_out[(size_t)(t0 + c0 + i) * H * Dv + (size_t)h * Dv + col] = oq[c];
+                }
+            }
         }
         __syncthreads();            // the buffer is free for the copy after next
     }
     if (ASYNC) cp_async_wait<0>();
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-        const int d = r * NPT + i;
-        if (active && d < D) S_base[(size_t)d * Dv + col] = S[i];
-    }
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+        for (int i = 0; i < NPT; ++i) {
+            const int d = r * NPT + i, col = col0 + col_local + c * tcols;
+            if (col < Dv && d < D) S_base[(size_t)d * Dv + col] = S[c][i];
+        }
 }
 
 template <typename T>
@@ -282,14 +305,14 @@ __global__ void __launch_bounds__(128) delta_output_kernel(const float *__restri
     }
 }
 
-template <int NPT, bool ASYNC>
+template <int NPT, bool ASYNC, int NC>
 int launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const float *qkv_c, const float *gb, float *state, long long state_stride,
                 const int *seq_start, const int *slots, float *o_out, int H, int G, int D, int Dv, int R) {
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<NPT, ASYNC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<NPT, ASYNC, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LGML_FAIL("delta_scan: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
-    lgml_launch(delta_scan_kernel<NPT, ASYNC>, grid, SCAN_THREADS, smem, stream, qkv_c, gb, state, state_stride, seq_start, slots, o_out, H, G, D,
+    lgml_launch(delta_scan_kernel<NPT, ASYNC, NC>, grid, SCAN_THREADS, smem, stream, qkv_c, gb, state, state_stride, seq_start, slots, o_out, H, G, D,
                 Dv, R);
     return lgml_launch_status("delta_scan");
 }
@@ -326,12 +349,21 @@ LGML_API int lgml_delta_scan(const float *qkv_c, const float *gb, float *state, 
     while (R < 32 && (D + R - 1) / R > 16) R *= 2;       // 16 rows a thread while 32 threads a column suffice
     const int rows = (D + R - 1) / R;
     const int npt = rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
-    const int cols = SCAN_THREADS / R;
+    // Two columns a thread where a head has them, a thread's rows are few enough for the registers, and
+    // the grid still covers the SMs twice (many requests in a step: 30.8 us against 33.8 for 8 requests of
+    // 16 heads of 128 x 128).  One request's prompt is a chain per column, and half as many warps each
+    // with two chains were slower there (1.14 ms against 0.97 for 2,048 tokens), so it keeps one.
+    const int tcols = SCAN_THREADS / R;
+    const bool wide = npt <= 16 && Dv >= 2 * tcols && (long long)n_seqs * H * ((Dv + 2 * tcols - 1) / (2 * tcols)) >= 2 * 148;
+    const int nc = wide ? 2 : 1;
+    const int cols = nc * (SCAN_THREADS / R);
     const bool async = D % 4 == 0 && Dv % 4 == 0 && (((uintptr_t)qkv_c | (uintptr_t)gb) & 15) == 0;
     const size_t smem = sizeof(float) * (size_t)(async ? 2 : 1) * TCH * (3 * (size_t)(npt + 4) * R + 4 + cols);
     dim3 grid(n_seqs, H, (Dv + cols - 1) / cols);
 #define LGML_SCAN_ARGS grid, smem, stream, qkv_c, gb, state, state_stride, seq_start, slots, o_out, H, G, D, Dv, R
-#define LGML_SCAN_CASE(N) return async ? launch_scan<N, true>(LGML_SCAN_ARGS) : launch_scan<N, false>(LGML_SCAN_ARGS);
+#define LGML_SCAN_CASE(N)                                                                                          \
+    if (nc == 2) return async ? launch_scan<N, true, 2>(LGML_SCAN_ARGS) : launch_scan<N, false, 2>(LGML_SCAN_ARGS); \
+    return async ? launch_scan<N, true, 1>(LGML_SCAN_ARGS) : launch_scan<N, false, 1>(LGML_SCAN_ARGS);
     switch (npt) {
         case 4: LGML_SCAN_CASE(4)
         case 8: LGML_SCAN_CASE(8)

@@ -30,6 +30,8 @@ from .runner import ModelRunner
 from .runtime import MAX_RESULT
 from .scheduler import REPEAT_STOP, UBATCH, GenRequest, Scheduler
 
+DEFAULT_CTX = 4096      # context of a model whose configuration names no limit of positions, when none is given
+
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32}
 
 
@@ -59,7 +61,7 @@ class Engine:
         # a configuration that names no limit of positions is bounded by n_ctx alone
         max_pos = getattr(cfg, "max_position_embeddings", None) or None
         if n_ctx is None and max_pos is None:
-            raise ValueError("this configuration names no max_position_embeddings: give n_ctx")
+            n_ctx = DEFAULT_CTX          # a design without a limit of positions, and none asked for
         n_ctx = min(n_ctx or max_pos, max_pos or n_ctx)
         max_pos = max_pos or n_ctx
         self.n_ctx = n_ctx

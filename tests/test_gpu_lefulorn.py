@@ -212,6 +212,35 @@ def test_delta_scan_in_pieces_matches_the_plain_recurrence(D, Dv, Hh, G):
             assert float((got - want).abs().max()) < 1e-5
 
 
+def test_delta_scan_of_many_requests_at_once():
+    """48 requests of three tokens in one launch (the kernel then gives a thread two columns of the
+    state; 96 value columns leave the last block's second columns empty), a second launch on the
+    states the first left, against the plain recurrence over all six tokens."""
+    from lgml_b200 import ops
+
+    torch.manual_seed(6)
+    n_req, Hh, G, D, Dv = 48, 4, 2, 64, 96
+    q = torch.nn.functional.normalize(torch.randn(n_req, 6, G, D, dtype=F64), dim=-1) * D ** -0.5
+    k = torch.nn.functional.normalize(torch.randn(n_req, 6, G, D, dtype=F64), dim=-1)
+    v = torch.randn(n_req, 6, Hh, Dv, dtype=F64)
+    beta = torch.rand(n_req, 6, Hh, dtype=F64)
+    decay = torch.rand(n_req, 6, Hh, D, dtype=F64) ** 0.3
+    state = torch.zeros(n_req + 2, Hh * D * Dv, dtype=torch.float32, device=DEV)
+    slots = torch.randperm(n_req + 2)[:n_req].to(torch.int32).to(DEV)
+    starts = torch.arange(0, 3 * n_req + 1, 3, dtype=torch.int32, device=DEV)
+    outs = []
+    for lo in (0, 3):
+        sl = slice(lo, lo + 3)
+        qkv = torch.cat([q[:, sl].reshape(n_req * 3, -1), k[:, sl].reshape(n_req * 3, -1), v[:, sl].reshape(n_req * 3, -1)], 1).float().to(DEV).contiguous()
+        gb = torch.cat([decay[:, sl], beta[:, sl, :, None], torch.zeros(n_req, 3, Hh, 3, dtype=F64)], 3).reshape(n_req * 3, Hh, D + 4).float().to(DEV).contiguous()
+        outs.append(ops.delta_scan(qkv, gb, state, starts, slots, Hh, G, D, Dv).cpu().view(n_req, 3, Hh, Dv))
+    got = torch.cat(outs, 1).double()
+    for s in (0, 17, 47):
+        for h in range(Hh):
+            want = P.gated_delta_rule(q[s, :, h // 2], k[s, :, h // 2], v[s, :, h], beta[s, :, h], decay[s, :, h])
+            assert float((got[s, :, h] - want).abs().max()) < 1e-5
+
+
 @pytest.mark.parametrize("taps", [1, 2, 5])
 def test_delta_prepare_carries_the_filter_inputs_across_portions(taps):
     from lgml_b200 import ops
@@ -409,3 +438,18 @@ def test_trace_run_as_a_process(model, tmp_path):
             fed[e["id"]] += len(e["tokens"])
         assert r == rows.shape[0]
     L.compare(got, cfg, weights, seqs, **TOL["float32"])
+
+
+def test_command_line_generates_with_the_folders_architecture(model):
+    """python -m lgml_b200 on a Lefulorn folder (no context given: the design names no limit): greedy ids as the plain model's."""
+    name, cfg, made = model
+    weights, folder = made["float32"]
+    prompt = H.random_ids(19, cfg["vocab"], 400)
+    proc = subprocess.run([sys.executable, "-m", "lgml_b200", "-m", str(folder), "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)),
+                           "-n", "5", "--temperature", "0", "--repeat-stop", "0"], capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    got = [int(t) for t in proc.stdout.strip().splitlines()[-1].split(",")]
+    assert len(got) == 5
+    for i, tok in enumerate(got):
+        row = L.oracle_logits(cfg, weights, prompt + got[:i])[-1]
+        assert float(row.max() - row[tok]) <= 1e-4
