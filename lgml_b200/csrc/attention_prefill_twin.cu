@@ -248,11 +248,16 @@ __device__ __forceinline__ void write_p(const uint32_t (&r)[PAGE], uint32_t s_ad
 
 // D: the head size, 64 or 128 (a page of one head is then whole 64 x 64 boxes of the cache tensor).
 // tt: tokens per tile (128 / hpc); a CTA's tile of the list holds up to 2 tt tokens.
-template <int D>
+// BIAS: the form with a distance bias, a sink and an output gate.  Head h's scores lose
+// slopes[h] * (query position - key position); its denominator gains exp(sinks[h]) once; the
+// normalised output is multiplied by sigmoid(gate) (float32 [tokens, H D], row stride ldg).  Each
+// of the three pointers may be null.  Without BIAS none of it is compiled in.
+template <int D, bool BIAS>
 __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const __nv_bfloat16 *__restrict__ q, int ldq,
     const int *__restrict__ positions, const int *__restrict__ tiles, const int *__restrict__ block_table, int max_blocks, int n_pages,
-    __nv_bfloat16 *__restrict__ out, int ldo, int H, int Hkv, int hpc, int tt, float scale, int window, int *__restrict__ status) {
+    __nv_bfloat16 *__restrict__ out, int ldo, int H, int Hkv, int hpc, int tt, float scale, int window, int *__restrict__ status,
+    const float *__restrict__ slopes, const float *__restrict__ sinks, const float *__restrict__ gate, int ldg) {
     constexpr int KB = D / 64;                              // 64-element blocks along the head dimension
     constexpr uint32_t TILE_BYTES = KB * ROWS * 128;        // the queries of one tile: [KB][128 rows][128 B]
     constexpr uint32_t PAGE_BYTES = KB * PAGE * 128;        // a page of keys [KB][64 keys][128 B] (K-major: row = key), or of values (N-major: 64 dims per row)
@@ -283,6 +288,11 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
     const int lo_first = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
     const int pg_lo = lo_first / PAGE, pg_hi = pos_last / PAGE;
     const int n_steps = pg_hi - pg_lo + 1;                        // a page a step
+    // BIAS walks the pages from the newest to the oldest: the bias falls with a key's age (by 64
+    // slopes a page), so a row's maximum is as good as settled on its first page; walking up,
+    // a head with a steep slope would have to correct its output on every page.
+    auto page_index = [&](int j) -> int { return BIAS ? pg_hi - j : pg_lo + j; };
+    const int j_fix = BIAS ? 0 : n_steps - 1;                     // the step of the page that holds the last key
     const int n_act = n_tok > tt ? 2 : 1;                         // tiles that hold tokens
     const float scale_log2 = scale * 1.4426950408889634f;
     // The last page's values behind the last key may be anything, NaN included, and 0 x NaN is
@@ -342,7 +352,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
     // A page the table does not name is an error of the caller: the status word says so (3), the
     // host raises, and page 0 is read in its place.
     auto page_of = [&](int j) -> int {
-        const int page = table[pg_lo + j];
+        const int page = table[page_index(j)];
         if (page >= 0 && page < n_pages) return page;
         atomicExch(status, 3);
         return 0;
@@ -388,13 +398,16 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
         const int qpos = row_valid ? pos_first_t + my_tok : -1;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)t * TILE_COLS;
         const uint32_t o_addr = lane_addr + O_COL;
+        // base-2 units, as the scores: the slope of this row's head and its sink
+        const int my_head = kvh * group + g0 + (my_g < g_count ? my_g : 0);
+        const float slope2 = (BIAS && slopes) ? slopes[my_head] * 1.4426950408889634f : 0.f;
         // m_ref: the maximum (base-2 units) that this row's sum l_run and its output in tensor memory
         // are relative to.  It follows the row's running maximum only when that has grown by more
         // than RESCALE_STEP since.
         float m_ref = -INFINITY, l_run = 0.f;
         bool alive = t < n_act;
         for (int j = 0; alive && j < n_steps; ++j) {
-            const int key0 = (pg_lo + j) * PAGE, b = j & 1;
+            const int key0 = page_index(j) * PAGE, b = j & 1;
             const uint32_t s_addr = lane_addr + (uint32_t)b * PAGE;
             if (!warp_wait(&s_full[t][b], (j >> 1) & 1, abort_flag, status)) {
                 alive = false;
@@ -410,6 +423,20 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
 #pragma unroll
             for (int c0 = 0; c0 < PAGE; c0 += 16) tcgen05_ld_16(s_addr + (uint32_t)c0, *reinterpret_cast<uint32_t(*)[16]>(&r[c0]));
             tcgen05_wait_ld();
+            // BIAS: r becomes the scaled score plus the part of the bias that depends on the key,
+            // slope (key - key0); what depends on the row only, - slope (qpos - key0), is row_bias
+            float row_bias = 0.f;
+            if (BIAS) {
+                row_bias = -slope2 * (float)(qpos - key0);
+                const float2 scale2 = make_float2(scale_log2, scale_log2), slope22 = make_float2(slope2, slope2);
+#pragma unroll
+                for (int c = 0; c < PAGE; c += 2) {
+                    const float2 x = fma2(make_float2(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2,
+                                          fma2(make_float2((float)c, (float)(c + 1)), slope22, make_float2(0.f, 0.f)));
+                    r[c] = __float_as_uint(x.x);
+                    r[c + 1] = __float_as_uint(x.y);
+                }
+            }
             // (four chains each: the order of a maximum or of these float32 partial sums is a
             //  function of the column only, so a row's result does not depend on the batch)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -428,7 +455,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // the scale is positive, so the maximum of the raw scores is the maximum of the scaled ones
-            const float m_new = mx * scale_log2;
+            const float m_new = BIAS ? mx + row_bias : mx * scale_log2;
             float corr = 1.f;
             if (m_ref == -INFINITY) {
                 m_ref = m_new;                       // nothing summed yet: nothing to correct
@@ -457,10 +484,11 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
                     tcgen05_st_16(o_addr + (uint32_t)c0, o);
                 }
             }
-            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;    // keeps (-inf) - (-inf) out of the exponent
+            const float neg_m = (m_ref == -INFINITY) ? 0.f : row_bias - m_ref;    // keeps (-inf) - (-inf) out of the exponent
             float2 sum4[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-            if (edge) write_p<true>(r, s_addr, scale_log2, neg_m, c_lo, c_hi, sum4);
-            else write_p<false>(r, s_addr, scale_log2, neg_m, c_lo, c_hi, sum4);
+            const float p_scale = BIAS ? 1.f : scale_log2;              // BIAS: r holds scaled scores already
+            if (edge) write_p<true>(r, s_addr, p_scale, neg_m, c_lo, c_hi, sum4);
+            else write_p<false>(r, s_addr, p_scale, neg_m, c_lo, c_hi, sum4);
             const float2 sum2 = add2(add2(sum4[0], sum4[1]), add2(sum4[2], sum4[3]));
             l_run += sum2.x + sum2.y;
             tcgen05_wait_st();
@@ -471,8 +499,11 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
         if (t < n_act) {
             if (alive && !warp_wait(&o_last[t], 0, abort_flag, status)) alive = false;
             tcgen05_fence_after();
-            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            // the sink: a term of the denominator without a key or a value
+            if (BIAS && sinks && m_ref != -INFINITY) l_run += ex2(sinks[my_head] * 1.4426950408889634f - m_ref);
+            const float inv = l_run > 0.f && l_run < INFINITY ? 1.f / l_run : 0.f;
             const bool store = row_valid && alive;
+            const float *grow = (BIAS && gate && store) ? gate + (size_t)(row0 + t * tt + my_tok) * ldg + (size_t)my_head * D : nullptr;
             // (every lane takes part in the loads from tensor memory, which are for whole warps; rows
             //  without a token only skip the stores)
             __nv_bfloat16 *dst = out + (size_t)(row0 + (store ? t * tt + my_tok : 0)) * ldo + (size_t)(kvh * group + g0 + (store ? my_g : 0)) * D;
@@ -485,9 +516,16 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
 #pragma unroll
                     for (int c8 = 0; c8 < 16; c8 += 8) {
                         uint32_t h[4];
+                        float gs[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+                        if (BIAS && grow) {
+                            const float4 ga = *reinterpret_cast<const float4 *>(grow + c0 + c8), gb = *reinterpret_cast<const float4 *>(grow + c0 + c8 + 4);
+                            const float gv[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) gs[i] = 1.0f / (1.0f + __expf(-gv[i]));
+                        }
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(o[c8 + 2 * i]) * inv, __uint_as_float(o[c8 + 2 * i + 1]) * inv);
+                            __nv_bfloat162 pr = __floats2bfloat162_rn(__uint_as_float(o[c8 + 2 * i]) * inv * gs[2 * i], __uint_as_float(o[c8 + 2 * i + 1]) * inv * gs[2 * i + 1]);
                             h[i] = *reinterpret_cast<uint32_t *>(&pr);
                         }
                         *reinterpret_cast<uint4 *>(dst + c0 + c8) = make_uint4(h[0], h[1], h[2], h[3]);
@@ -543,7 +581,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
         }
         for (int j = 0; alive && j < n_steps; ++j) {
             if (!mbar_wait(&v_full[j % STAGES], (j / STAGES) & 1, abort_flag, status)) break;
-            if (fix_last && j == n_steps - 1 && !mbar_wait(&v_fixed, 0, abort_flag, status)) break;
+            if (fix_last && j == j_fix && !mbar_wait(&v_fixed, 0, abort_flag, status)) break;
             if (!mbar_wait(&p_full[t][j & 1], (j >> 1) & 1, abort_flag, status)) break;
             tcgen05_fence_after();
             issue_output(j);
@@ -557,6 +595,9 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
         // ---- the later copies: a stage is free once the products that read it are done -----------------
         // (V(0 .. STAGES-3) and K(0 .. STAGES-1) went out above)
         bool alive = true;
+        // (BIAS: the page with the last key is the first one; its values went out above, and no
+        //  later copy can complete that phase of the barrier before this thread has issued it)
+        if (BIAS && fix_last && mbar_wait(&v_full[0], 0, abort_flag, status)) mbar_arrive(&v_landed);
         for (int j = STAGES - 2; alive && j < n_steps; ++j) {
             if (j >= STAGES && !mbar_wait(&v_empty[j % STAGES], ((j / STAGES) - 1) & 1, abort_flag, status)) break;
             copy_values(j);
@@ -568,7 +609,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
         }
         // the last page of values is there: the zeros behind its last key may be written
         // (this thread armed that phase of the barrier itself, so it cannot take an older one for it)
-        if (fix_last && mbar_wait(&v_full[(n_steps - 1) % STAGES], ((n_steps - 1) / STAGES) & 1, abort_flag, status)) mbar_arrive(&v_landed);
+        if (!BIAS && fix_last && mbar_wait(&v_full[(n_steps - 1) % STAGES], ((n_steps - 1) / STAGES) & 1, abort_flag, status)) mbar_arrive(&v_landed);
         // no copy of this CTA is in flight when it ends (all have landed long ago unless a wait ran out)
         for (int j = max(n_steps - STAGES, 0); j < n_steps; ++j) {
             mbar_wait(&k_full[j % STAGES], (j / STAGES) & 1, abort_flag, status);
@@ -576,7 +617,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
         }
     } else if (warp == HELP_WARP && fix_last) {
         // ---- zeros behind the last key of the last page's values: warp 11 ------------------------------
-        const int htid = lane, j = n_steps - 1;
+        const int htid = lane, j = j_fix;
         if (warp_wait(&v_landed, 0, abort_flag, status)) {
             const uint32_t dst = smem_u32(Vs + (j % STAGES) * PAGE_BYTES);
             for (int i = htid; i < (PAGE - last_rows) * CHUNKS_D; i += HELPERS) {
@@ -600,15 +641,16 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
 }
 
 // ---- host side ----------------------------------------------------------------------------------
-template <int D>
+template <int D, bool BIAS>
 int launch(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, const int *tiles, const int *block_table, int max_blocks,
            const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, __nv_bfloat16 *out, int ldo, int H, int Hkv, int hpc, int tt,
-           float scale, int window, int *status, cudaStream_t stream) {
+           float scale, int window, int *status, cudaStream_t stream, const float *slopes = nullptr, const float *sinks = nullptr,
+           const float *gate = nullptr, int ldg = 0) {
     constexpr int KB = D / 64;
     const size_t smem = 2 * (size_t)KB * ROWS * 128 + 2 * STAGES * (size_t)KB * PAGE * 128 + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attention_twin_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(prefill_attention_twin_kernel<D, BIAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LGML_FAIL("prefill_attention_twin: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
@@ -616,8 +658,8 @@ int launch(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, con
     int rc;
     if ((rc = lgml_make_page_map(&mk, k_pages, n_pages, Hkv, D, "prefill_attention_twin"))) return rc;
     if ((rc = lgml_make_page_map(&mv, v_pages, n_pages, Hkv, D, "prefill_attention_twin"))) return rc;
-    lgml_launch(prefill_attention_twin_kernel<D>, grid, THREADS, smem, stream, mk, mv, q, ldq, positions, tiles, block_table, max_blocks, n_pages,
-                out, ldo, H, Hkv, hpc, tt, scale, window, status);
+    lgml_launch(prefill_attention_twin_kernel<D, BIAS>, grid, THREADS, smem, stream, mk, mv, q, ldq, positions, tiles, block_table, max_blocks, n_pages,
+                out, ldo, H, Hkv, hpc, tt, scale, window, status, slopes, sinks, gate, ldg);
     return lgml_launch_status("prefill_attention_twin");
 }
 }  // namespace
@@ -654,6 +696,40 @@ LGML_API int lgml_prefill_attention_twin(const void *q, int ldq, const int *posi
     const __nv_bfloat16 *qq = (const __nv_bfloat16 *)q, *kk = (const __nv_bfloat16 *)k_pages, *vv = (const __nv_bfloat16 *)v_pages;
     __nv_bfloat16 *oo = (__nv_bfloat16 *)out;
     if (D == 64)
-        return launch<64>(grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, hpc, tile_tokens / 2, scale, window, status, stream);
-    return launch<128>(grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, hpc, tile_tokens / 2, scale, window, status, stream);
+        return launch<64, false>(grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, hpc, tile_tokens / 2, scale, window, status, stream);
+    return launch<128, false>(grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, hpc, tile_tokens / 2, scale, window, status, stream);
+}
+
+// The same kernel with a distance bias (slopes), a sink in the denominator (sinks) and an output
+// gate (float32 [tokens, H D], row stride ldg), each per head and each optional; keys and values
+// of one head size, 64 or 128.
+LGML_API int lgml_sink_attention_twin(const void *q, int ldq, const int *positions, const int *tiles, int n_tiles, const int *block_table,
+                                      int max_blocks, const void *k_pages, const void *v_pages, int n_pages, int page_size,
+                                      const float *slopes, const float *sinks, const float *gate, int ldg, void *out, int ldo, int H, int Hkv,
+                                      int D, float scale, int window, int *status, cudaStream_t stream) {
+    LGML_REQUIRE(n_tiles >= 0 && H > 0 && Hkv > 0 && max_blocks > 0 && n_pages > 0, "sink_attention_twin: bad sizes");
+    LGML_REQUIRE(page_size == PAGE, "sink_attention_twin: pages of %d tokens, this kernel takes %d", page_size, PAGE);
+    LGML_REQUIRE(H % Hkv == 0, "sink_attention_twin: %d heads are no multiple of %d KV heads", H, Hkv);
+    LGML_REQUIRE(D == 64 || D == 128, "sink_attention_twin: head_dim %d (this kernel takes 64 and 128)", D);
+    LGML_REQUIRE(window >= 0, "sink_attention_twin: bad window");
+    LGML_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0,
+                 "sink_attention_twin: q and out must be 16-byte aligned with row strides that are multiples of 8");
+    LGML_REQUIRE(((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0, "sink_attention_twin: the cache must be 16-byte aligned");
+    LGML_REQUIRE(gate == nullptr || (ldg >= H * D && ldg % 4 == 0 && ((uintptr_t)gate & 15) == 0),
+                 "sink_attention_twin: the gate must be 16-byte aligned with a row stride that is a multiple of 4 and at least H D");
+    if (n_tiles == 0) return 0;
+    const int group = H / Hkv;
+    int hpc, tile_tokens;
+    lgml_prefill_attention_twin_shape(group, &hpc, &tile_tokens);
+    const int chunks = (group + hpc - 1) / hpc;
+    LGML_REQUIRE((long long)Hkv * chunks <= 65535, "sink_attention_twin: too many heads");
+    LGML_REQUIRE(n_tiles <= 65535, "sink_attention_twin: %d tiles in one launch (at most 65535)", n_tiles);
+    dim3 grid(Hkv * chunks, n_tiles);
+    const __nv_bfloat16 *qq = (const __nv_bfloat16 *)q, *kk = (const __nv_bfloat16 *)k_pages, *vv = (const __nv_bfloat16 *)v_pages;
+    __nv_bfloat16 *oo = (__nv_bfloat16 *)out;
+    if (D == 64)
+        return launch<64, true>(grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, hpc, tile_tokens / 2, scale, window,
+                                status, stream, slopes, sinks, gate, ldg);
+    return launch<128, true>(grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, hpc, tile_tokens / 2, scale, window,
+                             status, stream, slopes, sinks, gate, ldg);
 }

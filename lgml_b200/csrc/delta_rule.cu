@@ -346,7 +346,10 @@ LGML_API int lgml_delta_scan(const float *qkv_c, const float *gb, float *state, 
     LGML_REQUIRE(H <= 65535, "delta_scan: too many heads");
     if (n_seqs == 0) return 0;
     int R = 1;
-    while (R < 32 && (D + R - 1) / R > 16) R *= 2;       // 16 rows a thread while 32 threads a column suffice
+    // 16 rows a thread while 32 threads a column suffice.  (More threads a column do not pay although one
+    // prompt leaves most warp slots empty: 2,048 tokens of 16 heads of 128 x 128 take 0.97 ms with 8
+    // threads a column, 1.02 with 16, 2.36 with 32.)
+    while (R < 32 && (D + R - 1) / R > 16) R *= 2;
     const int rows = (D + R - 1) / R;
     const int npt = rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
     // Two columns a thread where a head has them, a thread's rows are few enough for the registers, and

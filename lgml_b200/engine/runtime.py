@@ -113,7 +113,13 @@ class Runtime:
         with head sizes of their own) of the step's queries over the cache."""
         if (self.dtype == torch.bfloat16 and self.attention_backend != "ref" and batch.max_q_len > ops.DECODE_MAX_Q
                 and cache.k.shape[2] == 64 and cache.k.shape[3] <= 128 and cache.v.shape[3] <= 128):
-            # prompts and portions: tiles of 64 tokens on tensor cores
+            if ops.sink_twin_supports(q, out, cache.k, cache.v, gate):
+                # prompts and portions, keys and values of one head size (64 or 128): the two-tile tcgen05 kernel
+                hkv = cache.k.shape[1]
+                tiles = batch.attention_tiles(ops.prefill_twin_tile_tokens(n_heads, hkv))
+                return ops.sink_attention_twin(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window,
+                                               self.status, slopes=slopes, sinks=sinks, gate=gate)
+            # every other head size up to 128: tiles of 64 tokens, mma.sync
             tiles = batch.attention_tiles(ops.SINK_TILE_TOKENS)
             return ops.sink_attention_mma(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window,
                                           self.status, slopes=slopes, sinks=sinks, gate=gate)

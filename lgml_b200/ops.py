@@ -555,6 +555,57 @@ def sink_attention_mma(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Te
     return out
 
 
+def sink_twin_supports(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, gate: Optional[torch.Tensor]) -> bool:
+    """Whether ``sink_attention_twin`` takes these operands: pages of 64, keys and values of one head
+    size, 64 or 128, and q, out and the gate readable in 16-byte pieces."""
+    return (PREFILL_ATTENTION == "tcgen05" and k_pages.shape[2] == 64 and k_pages.shape[3] in (64, 128) and v_pages.shape[3] == k_pages.shape[3]
+            and prefill_tc_supports(q, out)
+            and (gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.stride(0) % 4 == 0 and gate.data_ptr() % 16 == 0)))
+
+
+def sink_attention_twin(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
+                        v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int, status: torch.Tensor,
+                        slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
+                        gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``sink_attention`` for prompts and portions on tcgen05 tensor cores: the two-tile kernel of
+    ``prefill_attention_twin`` with the slopes' bias on the scores, the sink in the denominator and
+    the gate on the output.  bfloat16, pages of 64, keys and values of one head size (64 or 128).
+    ``tiles`` as for ``prefill_attention_twin`` (``prefill_twin_tile_tokens``)."""
+    _need(q, "queries", torch.bfloat16, 2)
+    _need(out, "attention output", torch.bfloat16, 2)
+    ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
+    n = q.shape[0]
+    _need(k_pages, "key pages", torch.bfloat16, 4)
+    _need(v_pages, "value pages", torch.bfloat16, 4)
+    n_pages, hkv, page, d = k_pages.shape
+    _need(positions, "positions", torch.int32, 1)
+    _need(tiles, "tiles", torch.int32, 2)
+    _need(block_table, "block table", torch.int32, 2)
+    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * d) or tiles.shape[1] != 4 or v_pages.shape != k_pages.shape:
+        raise KernelError(f"sink_attention_twin: q {tuple(q.shape)} / out {tuple(out.shape)} / tiles {tuple(tiles.shape)} / values "
+                          f"{tuple(v_pages.shape)} do not fit")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous() or not tiles.is_contiguous():
+        raise KernelError("sink_attention_twin: pages, block table and tiles must be contiguous")
+    for t, what in ((slopes, "slopes"), (sinks, "sinks")):
+        if t is not None:
+            _need(t, what, torch.float32, 1)
+            if t.numel() != n_heads or not t.is_contiguous():
+                raise KernelError(f"sink_attention_twin: one of the {what} per head")
+    ldg = 0
+    if gate is not None:
+        _need(gate, "gate", torch.float32, 2)
+        ldg = _rows_contiguous(gate, "gate")
+        if tuple(gate.shape) != (n, n_heads * d):
+            raise KernelError(f"sink_attention_twin: gate {tuple(gate.shape)} is not [{n}, {n_heads * d}]")
+    fn = _fn("attention_prefill_twin", "lgml_sink_attention_twin", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                                                    c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                                                    c_int, c_float, c_int, c_void_p, c_void_p])
+    _check("attention_prefill_twin", fn(_ptr(q), ldq, _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(block_table), block_table.shape[1],
+                                        _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), ldo,
+                                        n_heads, hkv, d, float(scale), int(window or 0), _ptr(status), _stream()), "sink_attention_twin")
+    return out
+
+
 def sink_decode_splits(n_tokens: int, n_kv_heads: int, group: int, reach: int) -> int:
     """Key ranges of the split sink attention: enough CTAs to cover the SMs twice, at least two pages
     a range, at most 64 ranges, and none of them empty.  ``reach``: the most keys a query sees."""

@@ -62,8 +62,18 @@ ONLY_ATTENTION = config(83, 48, [
     attention(4, 2, 16, 8, scale=0.3, v_mix=True, ff=24),
 ], eps=1e-5, logit_scale=1.0)
 
+# Keys and values of one head size, 64 or 128: prompts and portions of these layers run on the
+# two-tile tcgen05 attention kernel (groups of 2, 1 and 3 heads; windows across pages and none).
+WIDE_HEADS = config(101, 96, [
+    attention(4, 2, 64, 64, scale=0.15, window=100, q_temp=(0.3, 16), v_mix=True, ff=72),
+    delta(2, 1, 32, 64, conv=3),
+    attention(2, 2, 128, 128, scale=0.1),
+    attention(6, 2, 64, 64, scale=0.15, window=40, v_mix=True),
+], eps=1e-5, logit_scale=0.7)
+WIDE_HEADS_RANKS = {1: (8, 16)}
+
 CONFIGS = {"mixed": (MIXED, MIXED_RANKS), "odd": (ODD, ODD_RANKS), "only_delta": (ONLY_DELTA, ONLY_DELTA_RANKS),
-           "only_attention": (ONLY_ATTENTION, {})}
+           "only_attention": (ONLY_ATTENTION, {}), "wide_heads": (WIDE_HEADS, WIDE_HEADS_RANKS)}
 
 
 def random_weights(cfg: dict, ranks: Dict[int, Tuple[int, int]], seed: int, sharpen: float = 1.0) -> Dict[str, torch.Tensor]:

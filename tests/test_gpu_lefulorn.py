@@ -62,6 +62,12 @@ def run_sink_attention(q, k, v, sink, scale, window, dtype, temp=None, gate=None
     if mma == "split":      # the split form for decoding, here on every token of the run
         ops.sink_decode(qd, positions, seq, table, kp, vp, out, Hh, scale, window or 0, status, 3, slopes=slopes,
                         sinks=sink.float().to(DEV), gate=gate)
+    elif mma == "twin":      # the two-tile tcgen05 form: tiles of 2 x (128 rows / heads of a KV head) tokens
+        tt = ops.prefill_twin_tile_tokens(Hh, G)
+        tiles = torch.tensor([[0, r0, min(tt, T - r0), 0] for r0 in range(0, T, tt)], dtype=torch.int32, device=DEV)
+        assert ops.sink_twin_supports(qd, out, kp, vp, gate)
+        ops.sink_attention_twin(qd, positions, tiles, table, kp, vp, out, Hh, scale, window or 0, status, slopes=slopes,
+                                sinks=sink.float().to(DEV), gate=gate)
     elif mma:     # the tensor-core form: tiles of at most 64 tokens, here 64, 64, ..., and the rest
         tiles = torch.tensor([[0, r0, min(64, T - r0), 0] for r0 in range(0, T, 64)], dtype=torch.int32, device=DEV)
         ops.sink_attention_mma(qd, positions, tiles, table, kp, vp, out, Hh, scale, window or 0, status, slopes=slopes,
@@ -108,6 +114,42 @@ def test_sink_attention_edges_of_the_window_and_far_keys(dtype, window, sizes):
         one_more = P.sink_attention(q, k, v, sink, 0.7, window + 1, P.distance_slopes(Hh))
         one_less = P.sink_attention(q, k, v, sink, 0.7, window - 1, P.distance_slopes(Hh))
         assert float((one_more - want).abs().max()) > 5 * tol and float((one_less - want).abs().max()) > 5 * tol
+
+
+@pytest.mark.parametrize("window", [None, 1, 5, 64, 70, 129, 200])
+@pytest.mark.parametrize("shape", [(6, 2, 64), (5, 5, 128), (12, 1, 64)])
+def test_sink_attention_on_tcgen05_edges_sink_and_gate(window, shape):
+    """The two-tile tcgen05 form (keys and values of one head size, 64 or 128; groups of 3, 1 and 12
+    heads): 330 tokens that start at position 21, the keys at a window's edge (or key 3 without one)
+    ranking highest, sinks from small to as large as the largest score, the gate read from a column slice."""
+    torch.manual_seed(8)
+    Hh, G, D = shape
+    T, pos0 = 330, 21
+    q = torch.randn(T, Hh, D, dtype=F64) * 0.2
+    k = torch.randn(T, G, D, dtype=F64) * 0.2
+    v = torch.randn(T, G, D, dtype=F64)
+    q[:, :, 0] = 1.0
+    k[:, :, 0] = 0.0
+    if window is None:
+        k[3, :, 0] = 40.0
+    else:
+        for j in range(T):
+            k[j, :, 0] = 20.0 * ((T - 1 - j) % (window + 1)) / (window + 1)
+    q, k, v = (t.to(torch.bfloat16).double() for t in (q, k, v))
+    sink = torch.linspace(-2.0, 12.0, Hh, dtype=F64)        # the last head's sink stands beside the edge keys' scores
+    wide = torch.randn(T, Hh * D + 8, dtype=torch.float32, device=DEV)
+    gate = wide[:, 4:4 + Hh * D]
+    got = run_sink_attention(q, k, v, sink, 0.6, window, torch.bfloat16, pos0=pos0, gate=gate, mma="twin")
+    # the cells before the portion are zero keys and values: score 0 minus the distance bias
+    z = lambda t: torch.cat([torch.zeros(pos0, *t.shape[1:], dtype=F64), t])
+    want = P.sink_attention(z(q), z(k), z(v), sink, 0.6, window, P.distance_slopes(Hh))[pos0:]
+    want = want * torch.sigmoid(gate.double().cpu()).view(T, Hh, D)
+    assert float((got - want).abs().max()) < 2e-2, float((got - want).abs().max())
+    if window not in (None, 1):
+        one_more = P.sink_attention(z(q), z(k), z(v), sink, 0.6, window + 1, P.distance_slopes(Hh))[pos0:] * torch.sigmoid(gate.double().cpu()).view(T, Hh, D)
+        assert float((one_more - want).abs().max()) > 0.05          # one key more would show
+    no_sink = P.sink_attention(z(q), z(k), z(v), torch.full((Hh,), -1e9, dtype=F64), 0.6, window, P.distance_slopes(Hh))[pos0:]
+    assert float((no_sink * torch.sigmoid(gate.double().cpu()).view(T, Hh, D) - want).abs().max()) > 0.05
 
 
 def test_sink_share_temperature_mixing_and_gate():
