@@ -18,9 +18,8 @@
 //   delta_conv_state   per request: the slot's last taps - 1 inputs after this step
 //   delta_scan         per (request, head, group of value columns): the recurrence over the
 //                      request's tokens in order.  A thread owns a run of consecutive rows of one
-//                      column of S in registers.  With S' = g S the read-out is S'^T q + u (k . q),
-//                      so the R threads of a column add up S'^T k, S'^T q and k . q in one round of
-//                      shuffles, in a fixed order.  Columns never talk to each other, so the
+//                      column of S in registers; the R threads of a column add up S^T k and S^T q
+//                      by shuffles in a fixed order.  Columns never talk to each other, so the
 //                      result does not depend on how a prompt was cut or what else is in the batch.
 //   delta_output       per (token, head): o / rms(o) * weight * sigmoid(gate)
 #include <math.h>
@@ -224,81 +223,52 @@ __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(
         }
         __syncthreads();
         const float *k_s = buf, *q_s = k_s + TCH * DP, *g_s = q_s + TCH * DP, *v_s = g_s + TCH * GP;
-        // A token's operands in registers: this thread's runs of k, q and the decays (16-byte reads),
-        // its columns' values and beta.  Token i + 1 is fetched while token i is computed.
-        auto fetch = [&](int i, float (&kk)[NPT], float (&qq)[NPT], float (&gg)[NPT], float (&vv)[NC], float &beta) {
+        for (int i = 0; i < nt; ++i) {
+            // this thread's runs of k, q and the decays, in registers by 16-byte reads
+            float kk[NPT], qq[NPT], gg[NPT];
 #pragma unroll
             for (int j = 0; j < NPT; j += 4) {
                 *reinterpret_cast<float4 *>(kk + j) = *reinterpret_cast<const float4 *>(k_s + i * DP + r * RUN + j);
                 *reinterpret_cast<float4 *>(gg + j) = *reinterpret_cast<const float4 *>(g_s + i * GP + r * RUN + j);
                 *reinterpret_cast<float4 *>(qq + j) = *reinterpret_cast<const float4 *>(q_s + i * DP + r * RUN + j);
             }
-#pragma unroll
-            for (int c = 0; c < NC; ++c) vv[c] = v_s[i * cols + col_local + c * tcols];
-            beta = g_s[i * GP + DP];
-        };
-        // One token.  With S' = g S (decayed), the state after the write is S' + k u^T, so the read-out
-        // S^T q = S'^T q + u (k . q): the three sums k . S', q . S' and k . q go through the lanes
-        // together, one round of shuffles a token instead of two in a row, and nothing of the read-out
-        // stands between this token's write and the next token's decay.  Four partial sums each
-        // (NPT is a multiple of 4), added in a fixed order.
-        auto token = [&](int i, const float (&kk)[NPT], const float (&qq)[NPT], const float (&gg)[NPT], const float (&vv)[NC], float beta) {
-            float ks[NC], qs[NC], kq;
-            {
-                float a[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int j = 0; j < NPT; ++j) a[j & 3] = fmaf(kk[j], qq[j], a[j & 3]);
-                kq = (a[0] + a[1]) + (a[2] + a[3]);
-            }
+            // four partial sums each (NPT is a multiple of 4), added in a fixed order: the chain of
+            // dependent operations per token is a quarter as long, and the next token waits on it
+            float ks[NC], oq[NC];
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
-                float ka[4] = {0.f, 0.f, 0.f, 0.f}, qa[4] = {0.f, 0.f, 0.f, 0.f};
+                float ka[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int j = 0; j < NPT; ++j) {
                     S[c][j] *= gg[j];
                     ka[j & 3] = fmaf(kk[j], S[c][j], ka[j & 3]);
-                    qa[j & 3] = fmaf(qq[j], S[c][j], qa[j & 3]);
                 }
                 ks[c] = (ka[0] + ka[1]) + (ka[2] + ka[3]);
-                qs[c] = (qa[0] + qa[1]) + (qa[2] + qa[3]);
             }
+            for (int o = 1; o < R; o <<= 1)
 #pragma unroll
-            for (int lvl = 0; lvl < 5; ++lvl) {
-                const int o = 1 << lvl;
-                if (o < R) {
-#pragma unroll
-                    for (int c = 0; c < NC; ++c) ks[c] += __shfl_xor_sync(0xffffffffu, ks[c], o);
-                    kq += __shfl_xor_sync(0xffffffffu, kq, o);
-#pragma unroll
-                    for (int c = 0; c < NC; ++c) qs[c] += __shfl_xor_sync(0xffffffffu, qs[c], o);
-                }
-            }
+                for (int c = 0; c < NC; ++c) ks[c] += __shfl_xor_sync(0xffffffffu, ks[c], o);
+            const float beta = g_s[i * GP + DP];
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
-                const float u = beta * (vv[c] - ks[c]);
+                const float u = beta * (v_s[i * cols + col_local + c * tcols] - ks[c]);
+                float qa[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int j = 0; j < NPT; ++j) S[c][j] = fmaf(kk[j], u, S[c][j]);
-                const int col = col0 + col_local + c * tcols;
-                if (r == 0 && col < Dv) o_out[(size_t)(t0 + c0 + i) * H * Dv + (size_t)h * Dv + col] = fmaf(u, kq, qs[c]);
-            }
-        };
-        constexpr bool AHEAD = NPT * NC <= 16;        // two tokens' operands fit the registers beside the state
-        if (AHEAD) {
-            float ka_[NPT], qa_[NPT], ga_[NPT], va_[NC], ba_, kb_[NPT], qb_[NPT], gb_[NPT], vb_[NC], bb_ = 0.f;
-            fetch(0, ka_, qa_, ga_, va_, ba_);
-            for (int i = 0; i < nt; i += 2) {
-                if (i + 1 < nt) fetch(i + 1, kb_, qb_, gb_, vb_, bb_);
-                token(i, ka_, qa_, ga_, va_, ba_);
-                if (i + 1 < nt) {
-                    if (i + 2 < nt) fetch(i + 2, ka_, qa_, ga_, va_, ba_);
-                    token(i + 1, kb_, qb_, gb_, vb_, bb_);
+                for (int j = 0; j < NPT; ++j) {
+                    S[c][j] = fmaf(kk[j], u, S[c][j]);
+                    qa[j & 3] = fmaf(qq[j], S[c][j], qa[j & 3]);
                 }
+                oq[c] = (qa[0] + qa[1]) + (qa[2] + qa[3]);
             }
-        } else {
-            for (int i = 0; i < nt; ++i) {
-                float ka_[NPT], qa_[NPT], ga_[NPT], va_[NC], ba_;
-                fetch(i, ka_, qa_, ga_, va_, ba_);
-                token(i, ka_, qa_, ga_, va_, ba_);
+            for (int o = 1; o < R; o <<= 1)
+#pragma unroll
+                for (int c = 0; c < NC; ++c) oq[c] += __shfl_xor_sync(0xffffffffu, oq[c], o);
+            if (r == 0) {
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    const int col = col0 + col_local + c * tcols;
+                    if (col < Dv) o_out[(size_t)(t0 + c0 + i) * H * Dv + (size_t)h * Dv + col] = oq[c];
+                }
             }
         }
         __syncthreads();            // the buffer is free for the copy after next
@@ -376,11 +346,11 @@ LGML_API int lgml_delta_scan(const float *qkv_c, const float *gb, float *state, 
     LGML_REQUIRE(H <= 65535, "delta_scan: too many heads");
     if (n_seqs == 0) return 0;
     int R = 1;
-    // Threads a column: 8 rows a thread up to 16 threads, then 16 rows a thread up to 32.  One prompt
-    // leaves most warp slots empty whatever the split (2,048 tokens of 16 heads of 128 x 128: 0.91 ms
-    // with 4 threads a column, 0.97 with 8, 0.87 with 16, 1.74 with 32, where a block of 4 columns
-    // stages all of k, q and the decays for itself); a decode step of 8 requests takes the same with 8 and 16.
-    while (R < 16 && (D + R - 1) / R > 8) R *= 2;
+    // 16 rows a thread while 32 threads a column suffice.  (More threads a column do not pay although one
+    // prompt leaves most warp slots empty: 2,048 tokens of 16 heads of 128 x 128 take 0.97 ms with 8
+    // threads a column, 1.02 with 16, 2.36 with 32.  Every block walks the whole chain of tokens, so
+    // the blocks must all be resident at once: with 32 such heads, 16 threads a column made 512 blocks
+    // where 444 fit, and the prompt took twice as long.)
     while (R < 32 && (D + R - 1) / R > 16) R *= 2;
     const int rows = (D + R - 1) / R;
     const int npt = rows <= 4 ? 4 : rows <= 8 ? 8 : rows <= 16 ? 16 : 32;
