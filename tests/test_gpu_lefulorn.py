@@ -398,7 +398,7 @@ def test_all_cuttings_match_the_plain_model(model, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_then_long_decoding_over_every_window(model, dtype):
     """Three tokens of prompt, then 180 tokens one by one (through captured steps): every window of
-    the models (1, 3, 20, 65, 70) passes over decoded tokens, and the state is carried 180 times."""
+    the models (1, 3, 20, 40, 65, 70, 100) passes over decoded tokens, and the state is carried 180 times."""
     name, cfg, made = model
     weights, folder = made[dtype]
     seqs = sequences(cfg, [183], seed=70)
