@@ -42,13 +42,19 @@ PAGE_SIZE = 64  # tokens per page: BLOCK of lua/lgml/transformer.lua:30
 
 @dataclass(frozen=True)
 class PagedKV:
-    """Keys and values of every position (window None) or of the last ``window``.  Values
-    have the keys' head size unless ``v_head_dim`` gives their own."""
+    """Keys and values of every position (window None) or of the last ``window`` and the
+    request's first ``keep_first``.  Values have the keys' head size unless ``v_head_dim`` gives
+    their own, and the keys' head count unless ``v_heads`` does (several key heads on one value
+    head).  ``v_in_k``: the values are the first ``v_head_dim`` entries of the key cells and take
+    no pages of their own (a mixer whose keys extend its values)."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    keep_first: int = 0
+    v_heads: Optional[int] = None
+    v_in_k: bool = False
 
 
 @dataclass(frozen=True)
@@ -118,9 +124,10 @@ class CacheManager:
                 if spec not in by_spec:
                     pages = n_pages
                     if spec.window is not None:
-                        # a request holds at most the window plus one step's tokens, rounded out to pages
+                        # a request holds at most the window plus one step's tokens, rounded out to pages,
+                        # and the pages of its kept first tokens
                         span = spec.window + (max_step_tokens or page_size)
-                        pages = min(n_pages, max_slots * (-(-span // page_size) + 1))
+                        pages = min(n_pages, max_slots * (-(-span // page_size) + 1 + -(-spec.keep_first // page_size)))
                     by_spec[spec] = len(self.groups)
                     self.groups.append(PagedGroup(spec, [], PagePool(pages)))
                 g = by_spec[spec]
@@ -138,10 +145,13 @@ class CacheManager:
                 raise TypeError(f"layer {layer}: unknown cache spec {spec!r}")
         for grp in self.groups:
             shape = (grp.pool.n_pages, grp.spec.n_kv_heads, page_size, grp.spec.head_dim)
-            v_shape = shape[:3] + (grp.spec.v_head_dim or grp.spec.head_dim,)
+            v_dim = grp.spec.v_head_dim or grp.spec.head_dim
+            v_shape = (shape[0], grp.spec.v_heads or grp.spec.n_kv_heads, page_size, v_dim)
+            if grp.spec.v_in_k and (v_dim > grp.spec.head_dim or v_shape[1] != grp.spec.n_kv_heads):
+                raise ValueError(f"values inside the key cells need the keys' head count and at most their size: {grp.spec}")
             for layer in grp.layers:
                 grp.k[layer] = torch.zeros(shape, dtype=dtype, device=self.device)
-                grp.v[layer] = torch.zeros(v_shape, dtype=dtype, device=self.device)
+                grp.v[layer] = grp.k[layer][..., :v_dim] if grp.spec.v_in_k else torch.zeros(v_shape, dtype=dtype, device=self.device)
         for sg in self.state_groups:
             for layer in sg.layers:
                 sg.state[layer] = torch.zeros((max_slots,) + tuple(sg.spec.shape), dtype=sg.spec.dtype, device=self.device)
@@ -168,7 +178,9 @@ class CacheManager:
     def bytes_held(self) -> int:
         n = 0
         for g in self.groups:
-            n += sum(t.numel() * t.element_size() for t in g.k.values()) + sum(t.numel() * t.element_size() for t in g.v.values())
+            n += sum(t.numel() * t.element_size() for t in g.k.values())
+            if not g.spec.v_in_k:
+                n += sum(t.numel() * t.element_size() for t in g.v.values())
         for sg in self.state_groups:
             n += sum(t.numel() * t.element_size() for t in sg.state.values())
         return n
@@ -241,11 +253,15 @@ class CacheManager:
         return found
 
     def _first_needed_block(self, grp: PagedGroup, n_tokens: int) -> int:
-        """Lowest block that a query at position >= n_tokens can still reach."""
+        """Lowest block that the window of a query at position >= n_tokens can still reach."""
         if grp.spec.window is None:
             return 0
         lowest_pos = max(0, n_tokens - grp.spec.window + 1)
         return lowest_pos // self.page_size
+
+    def _kept_blocks(self, grp: PagedGroup) -> int:
+        """The blocks at a request's start that every later query reaches (its kept first tokens)."""
+        return -(-grp.spec.keep_first // self.page_size) if grp.spec.window is not None else 0
 
     def pages_missing(self, req: Request, n_new: int) -> int:
         """Pages of the tightest full-attention group that ``reserve(req, n_new)`` would take."""
@@ -269,9 +285,10 @@ class CacheManager:
             for gi, grp in enumerate(self.groups):
                 table = req.tables[gi]
                 first = self._first_needed_block(grp, req.n_tokens)
+                kept = self._kept_blocks(grp)
                 while len(table) < need_blocks:
                     b = len(table)
-                    if b < first:
+                    if kept <= b < first:
                         table.append(-1)       # the window never reaches this block
                         taken.append((gi, -1))
                     else:
@@ -321,7 +338,7 @@ class CacheManager:
                 continue
             first = self._first_needed_block(grp, req.n_tokens)
             table = req.tables[gi]
-            for b in range(min(first, len(table))):
+            for b in range(self._kept_blocks(grp), min(first, len(table))):
                 if table[b] >= 0:
                     grp.pool.release(table[b])
                     table[b] = -1

@@ -46,6 +46,8 @@ LIBRARIES: Dict[str, tuple] = {
     "attention_decode_noalloc": ("attention_decode_noalloc.cu", []),
     "attention_sink": ("attention_sink.cu", []),
     "delta_rule": ("delta_rule.cu", []),
+    "attention_heads": ("attention_heads.cu", []),
+    "moe": ("moe.cu", []),
 }
 
 _HEADERS = ["common.cuh", "page_map.cuh"]

@@ -31,12 +31,12 @@ template <typename T>
 __global__ void __launch_bounds__(ITEMS) sink_qkv_store_kernel(
     const float *__restrict__ proj, int ldp, T *__restrict__ q_out, int ldq, const int *__restrict__ positions,
     const int *__restrict__ seq_of_token, const int *__restrict__ block_table, int max_blocks, T *__restrict__ k_pages,
-    T *__restrict__ v_pages, int n_pages, int page_size, int H, int Hkv, int D, int Dv, float temp_coef, int temp_every,
+    T *__restrict__ v_pages, int n_pages, int page_size, int H, int Hkv, int Hv, int D, int Dv, float temp_coef, int temp_every,
     int v_mode, float *__restrict__ v_keep, const float *__restrict__ v_lambda, int write_kv, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
-    const int nq = H * D, nk = Hkv * D, nv = Hkv * Dv;
+    const int nq = H * D, nk = Hkv * D, nv = Hv * Dv;
     const int e = blockIdx.y * ITEMS + threadIdx.x;
     if (e >= nq + (write_kv ? nk + nv : 0)) return;
     const int pos = positions[t];
@@ -66,16 +66,16 @@ __global__ void __launch_bounds__(ITEMS) sink_qkv_store_kernel(
         const float lam = v_lambda[0];
         val = (1.0f - lam) * val + lam * act_load(v_keep + (size_t)t * nv + c);
     }
-    v_pages[(((size_t)page * Hkv + g) * page_size + (size_t)(pos % page_size)) * Dv + d] = from_f32<T>(val);
+    v_pages[(((size_t)page * Hv + g) * page_size + (size_t)(pos % page_size)) * Dv + d] = from_f32<T>(val);
 }
 
-template <typename T>
+template <typename T, typename TO>
 __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
     const T *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
     const int *__restrict__ block_table, int max_blocks, const T *__restrict__ k_pages, const T *__restrict__ v_pages,
     int n_pages, int page_size, const float *__restrict__ slopes, const float *__restrict__ sinks,
-    const float *__restrict__ gate, int ldg, T *__restrict__ out, int ldo, int H, int Hkv, int D, int Dv, float scale,
-    int window, int *__restrict__ status) {
+    const float *__restrict__ gate, int ldg, TO *__restrict__ out, int ldo, int H, int Hkv, int Hv, int D, int Dv, int ldv, float scale,
+    int window, int keep_first, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
     __shared__ float qs[MAX_D];
@@ -83,11 +83,14 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
     __shared__ float m_w[WARPS], l_w[WARPS];
     const int t = blockIdx.x, h = blockIdx.y;
     const int g = h / (H / Hkv);
+    const int gv = g / (Hkv / Hv);          // several key heads may share one value head
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int pos = positions[t];
     const int seq = seq_of_token[t];
     const int *table = block_table + (size_t)seq * max_blocks;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int n_first = keep_first < lo ? keep_first : lo;     // kept first tokens that the window does not hold anyway
+    const int n_keys = n_first + (pos - lo + 1);
     const float slope = slopes ? slopes[h] : 0.f;
 
     for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = to_f32(act_load(q + (size_t)t * ldq + (size_t)h * D + d));
@@ -98,7 +101,9 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
 
-    for (int j = lo + warp; j <= pos; j += WARPS) {
+    // the visible keys in order: the kept first tokens, then the window; warp w takes every WARPS-th
+    for (int i = warp; i < n_keys; i += WARPS) {
+        const int j = i < n_first ? i : lo + (i - n_first);
         const int blk = j / page_size;
         const int page = blk < max_blocks ? table[blk] : -1;
         if (page < 0 || page >= n_pages) {  // a cell the table does not hold: flag it, skip the key
@@ -106,6 +111,7 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
             continue;
         }
         const size_t cell = ((size_t)page * Hkv + g) * page_size + (size_t)(j % page_size);
+        const size_t vcell = ((size_t)page * Hv + gv) * page_size + (size_t)(j % page_size);
         float dot = 0.f;
         for (int d = lane; d < D; d += 32) dot = fmaf(qs[d], to_f32(act_load(k_pages + cell * D + d)), dot);
         const float s = warp_sum(dot) * scale - slope * (float)(pos - j);
@@ -114,9 +120,9 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
         const float p = expf(s - m_new);
         l = l * corr + p;
 #pragma unroll
-        for (int i = 0; i < MAX_D / 32; ++i) {
-            const int d = lane + 32 * i;
-            if (d < Dv) acc[i] = acc[i] * corr + p * to_f32(act_load(v_pages + cell * Dv + d));
+        for (int i2 = 0; i2 < MAX_D / 32; ++i2) {
+            const int d = lane + 32 * i2;
+            if (d < Dv) acc[i2] = acc[i2] * corr + p * to_f32(act_load(v_pages + vcell * ldv + d));
         }
         m = m_new;
     }
@@ -144,7 +150,7 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
         for (int w = 0; w < WARPS; ++w) o += acc_w[w][d] * f[w];
         o = lsum > 0.f ? o / lsum : 0.f;
         if (gate) o *= 1.0f / (1.0f + expf(-act_load(gate + (size_t)t * ldg + (size_t)h * Dv + d)));
-        out[(size_t)t * ldo + (size_t)h * Dv + d] = from_f32<T>(o);
+        out[(size_t)t * ldo + (size_t)h * Dv + d] = from_f32<TO>(o);
     }
 }
 
@@ -965,29 +971,30 @@ int launch_decode(dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat
 }
 }  // namespace
 
-// proj: float32 [n_tokens, ldp], columns q (H D) | k (Hkv D) | v (Hkv Dv) | anything else.
+// proj: float32 [n_tokens, ldp], columns q (H D) | k (Hkv D) | v (Hv Dv) | anything else.  Keys and values may have head
+// counts of their own (several key heads that share one value head).
 // v_keep: float32 [n_tokens, Hkv Dv], written (v_mode 1) or read (v_mode 2); v_lambda: one float32 on the device.
 LGML_API int lgml_sink_qkv_store(const float *proj, int ldp, void *q_out, int dtype, int ldq, const int *positions, const int *seq_of_token,
                                  const int *block_table, int max_blocks, void *k_pages, void *v_pages, int n_pages, int page_size,
-                                 int n_tokens, int H, int Hkv, int D, int Dv, float temp_coef, int temp_every, int v_mode, float *v_keep,
+                                 int n_tokens, int H, int Hkv, int Hv, int D, int Dv, float temp_coef, int temp_every, int v_mode, float *v_keep,
                                  const float *v_lambda, int write_kv, int *status, cudaStream_t stream) {
-    LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && D > 0 && Dv > 0 && page_size > 0 && max_blocks > 0, "sink_qkv_store: bad sizes");
-    LGML_REQUIRE(ldp >= H * D + Hkv * (D + Dv), "sink_qkv_store: row stride %d is below the q, k and v columns", ldp);
+    LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && Hv > 0 && D > 0 && Dv > 0 && page_size > 0 && max_blocks > 0, "sink_qkv_store: bad sizes");
+    LGML_REQUIRE(ldp >= H * D + (write_kv ? Hkv * D + Hv * Dv : 0), "sink_qkv_store: row stride %d is below the q, k and v columns", ldp);
     LGML_REQUIRE(ldq >= H * D, "sink_qkv_store: q row stride %d is below H D = %d", ldq, H * D);
     LGML_REQUIRE(temp_coef == 0.f || temp_every > 0, "sink_qkv_store: the temperature's step must be positive");
     LGML_REQUIRE(v_mode >= 0 && v_mode <= 2, "sink_qkv_store: unknown value mode %d", v_mode);
     LGML_REQUIRE(v_mode == 0 || v_keep != nullptr, "sink_qkv_store: value mode %d needs the kept values", v_mode);
     LGML_REQUIRE(v_mode != 2 || v_lambda != nullptr, "sink_qkv_store: mixing needs its weight");
     if (n_tokens == 0) return 0;
-    const int items = H * D + (write_kv ? Hkv * (D + Dv) : 0);
+    const int items = H * D + (write_kv ? Hkv * D + Hv * Dv : 0);
     dim3 grid(n_tokens, (items + ITEMS - 1) / ITEMS);
     if (dtype == LGML_F32)
         lgml_launch(sink_qkv_store_kernel<float>, grid, ITEMS, 0, stream, proj, ldp, (float *)q_out, ldq, positions, seq_of_token, block_table,
-                    max_blocks, (float *)k_pages, (float *)v_pages, n_pages, page_size, H, Hkv, D, Dv, temp_coef, temp_every, v_mode, v_keep,
+                    max_blocks, (float *)k_pages, (float *)v_pages, n_pages, page_size, H, Hkv, Hv, D, Dv, temp_coef, temp_every, v_mode, v_keep,
                     v_lambda, write_kv, status);
     else if (dtype == LGML_BF16)
         lgml_launch(sink_qkv_store_kernel<__nv_bfloat16>, grid, ITEMS, 0, stream, proj, ldp, (__nv_bfloat16 *)q_out, ldq, positions, seq_of_token,
-                    block_table, max_blocks, (__nv_bfloat16 *)k_pages, (__nv_bfloat16 *)v_pages, n_pages, page_size, H, Hkv, D, Dv, temp_coef,
+                    block_table, max_blocks, (__nv_bfloat16 *)k_pages, (__nv_bfloat16 *)v_pages, n_pages, page_size, H, Hkv, Hv, D, Dv, temp_coef,
                     temp_every, v_mode, v_keep, v_lambda, write_kv, status);
     else
         LGML_FAIL("sink_qkv_store: unknown type %d", dtype);
@@ -995,26 +1002,36 @@ LGML_API int lgml_sink_qkv_store(const float *proj, int ldp, void *q_out, int dt
 }
 
 // slopes, sinks: float32 [H] or null (no bias, no sink); gate: float32 [n_tokens, ldg] (column h Dv + d) or null.
+// Hv value heads (Hkv a multiple of it: key heads g Hkv / Hv ... share value head g), value rows ldv elements apart
+// (values that are a column range of wider cells), keep_first: the first tokens of a request that stay visible
+// beyond the window; out_dtype: the output's type (float32 for a caller that combines heads afterwards).
 LGML_API int lgml_sink_attention(const void *q, int dtype, int ldq, const int *positions, const int *seq_of_token, const int *block_table,
                                  int max_blocks, const void *k_pages, const void *v_pages, int n_pages, int page_size, const float *slopes,
-                                 const float *sinks, const float *gate, int ldg, void *out, int ldo, int n_tokens, int H, int Hkv, int D,
-                                 int Dv, float scale, int window, int *status, cudaStream_t stream) {
-    LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && D > 0 && Dv > 0 && page_size > 0 && max_blocks > 0, "sink_attention: bad sizes");
+                                 const float *sinks, const float *gate, int ldg, void *out, int out_dtype, int ldo, int n_tokens, int H, int Hkv,
+                                 int Hv, int D, int Dv, int ldv, float scale, int window, int keep_first, int *status, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && Hv > 0 && D > 0 && Dv > 0 && page_size > 0 && max_blocks > 0, "sink_attention: bad sizes");
     LGML_REQUIRE(H % Hkv == 0, "sink_attention: %d heads are no multiple of %d KV heads", H, Hkv);
+    LGML_REQUIRE(Hkv % Hv == 0, "sink_attention: %d key heads are no multiple of %d value heads", Hkv, Hv);
     LGML_REQUIRE(D <= MAX_D && Dv <= MAX_D, "sink_attention: head sizes %d and %d must be at most %d", D, Dv, MAX_D);
+    LGML_REQUIRE(ldv >= Dv, "sink_attention: value rows %d apart hold no %d values", ldv, Dv);
     LGML_REQUIRE(H <= 65535, "sink_attention: too many heads");
-    LGML_REQUIRE(window >= 0, "sink_attention: bad window");
+    LGML_REQUIRE(window >= 0 && keep_first >= 0, "sink_attention: bad window");
     LGML_REQUIRE(gate == nullptr || ldg >= H * Dv, "sink_attention: the gate's row stride %d is below H Dv", ldg);
+    LGML_REQUIRE(out_dtype == dtype || out_dtype == LGML_F32, "sink_attention: the output is the inputs' type or float32");
     if (n_tokens == 0) return 0;
     dim3 grid(n_tokens, H);
     if (dtype == LGML_F32)
-        lgml_launch(sink_attention_kernel<float>, grid, WARPS * 32, 0, stream, (const float *)q, ldq, positions, seq_of_token, block_table,
+        lgml_launch(sink_attention_kernel<float, float>, grid, WARPS * 32, 0, stream, (const float *)q, ldq, positions, seq_of_token, block_table,
                     max_blocks, (const float *)k_pages, (const float *)v_pages, n_pages, page_size, slopes, sinks, gate, ldg, (float *)out, ldo, H,
-                    Hkv, D, Dv, scale, window, status);
-    else if (dtype == LGML_BF16)
-        lgml_launch(sink_attention_kernel<__nv_bfloat16>, grid, WARPS * 32, 0, stream, (const __nv_bfloat16 *)q, ldq, positions, seq_of_token,
+                    Hkv, Hv, D, Dv, ldv, scale, window, keep_first, status);
+    else if (dtype == LGML_BF16 && out_dtype == LGML_F32)
+        lgml_launch(sink_attention_kernel<__nv_bfloat16, float>, grid, WARPS * 32, 0, stream, (const __nv_bfloat16 *)q, ldq, positions, seq_of_token,
                     block_table, max_blocks, (const __nv_bfloat16 *)k_pages, (const __nv_bfloat16 *)v_pages, n_pages, page_size, slopes, sinks,
-                    gate, ldg, (__nv_bfloat16 *)out, ldo, H, Hkv, D, Dv, scale, window, status);
+                    gate, ldg, (float *)out, ldo, H, Hkv, Hv, D, Dv, ldv, scale, window, keep_first, status);
+    else if (dtype == LGML_BF16)
+        lgml_launch(sink_attention_kernel<__nv_bfloat16, __nv_bfloat16>, grid, WARPS * 32, 0, stream, (const __nv_bfloat16 *)q, ldq, positions, seq_of_token,
+                    block_table, max_blocks, (const __nv_bfloat16 *)k_pages, (const __nv_bfloat16 *)v_pages, n_pages, page_size, slopes, sinks,
+                    gate, ldg, (__nv_bfloat16 *)out, ldo, H, Hkv, Hv, D, Dv, ldv, scale, window, keep_first, status);
     else
         LGML_FAIL("sink_attention: unknown type %d", dtype);
     return lgml_launch_status("sink_attention");

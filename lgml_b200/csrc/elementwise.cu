@@ -339,6 +339,35 @@ __global__ void __launch_bounds__(GROUP) rmsnorm_any_kernel(const Args a) {
         }
     }
 }
+
+// Dynamic tanh norm: y = tanh(alpha * pre * x) * w + b, element by element: no mean and no variance,
+// so a row needs no sum and a thread takes four consecutive elements of any row.  `alpha` is a
+// scalar on the device (a tensor of the model), `pre` a constant of the caller (the embedding's
+// scale when the norm follows the embedding; the scaled rows themselves are never needed).  The
+// residual add and the row list work as in RMSNorm: x[row] += delta first (the sum written back
+// unless rows are gathered).
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256) dyt_norm_kernel(const Args a, const float *__restrict__ shift, const float *__restrict__ alpha,
+                                                       float pre, int n_rows) {
+    pdl_trigger();
+    pdl_wait();
+    const int width = a.width, quads = (width + PER - 1) / PER;
+    const float al = __ldg(alpha) * pre;
+    const size_t total = (size_t)n_rows * quads;
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(it / quads), i = (int)(it - (size_t)r * quads) * PER;
+        const size_t src = a.rows ? (size_t)a.rows[r] : (size_t)r;
+        float *xr = a.x + src * width;
+        float v[PER], w[PER], b[PER], y[PER];
+        load_quad(xr, i, width, a.vec, v);
+        if (a.delta) add_delta<TD>(a, xr, reinterpret_cast<const TD *>(a.delta) + src * width, i, width, v);
+        load_quad_const(a.weight, i, width, a.vec, w);
+        load_quad_const(shift, i, width, a.vec, b);
+#pragma unroll
+        for (int q = 0; q < PER; ++q) y[q] = fmaf(tanhf(al * v[q]), w[q], b[q]);
+        store_quad(reinterpret_cast<TO *>(a.out) + (size_t)r * width, i, width, a.vec, y);
+    }
+}
 }  // namespace rms
 
 template <typename TD, typename TO>
@@ -452,6 +481,70 @@ LGML_API int lgml_silu_mul(const void *gu, void *act, int dtype, int n_tokens, i
     else
         LGML_FAIL("silu_mul: unknown type %d", dtype);
     return lgml_launch_status("silu_mul");
+}
+
+template <typename TD>
+static int dyt_dispatch(rms::Args &a, const TD *, const float *shift, const float *alpha, float pre, int out_dtype, int n_rows, cudaStream_t stream) {
+    const size_t total = (size_t)n_rows * ((a.width + 3) / 4);
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (out_dtype == LGML_F32) lgml_launch(rms::dyt_norm_kernel<TD, float>, blocks, threads, 0, stream, a, shift, alpha, pre, n_rows);
+    else lgml_launch(rms::dyt_norm_kernel<TD, __nv_bfloat16>, blocks, threads, 0, stream, a, shift, alpha, pre, n_rows);
+    return lgml_launch_status("dyt_norm");
+}
+
+// delta, rows: as for lgml_rmsnorm.  out may be float32 (a new residual stream) or bfloat16.
+LGML_API int lgml_dyt_norm(float *x, const void *delta, int delta_dtype, int n_parts, long long part_stride, const float *delta_bias,
+                           const float *weight, const float *shift, const float *alpha, float pre, const int *rows, void *out,
+                           int out_dtype, int n_rows, int width, cudaStream_t stream) {
+    LGML_REQUIRE(n_rows >= 0 && width > 0, "dyt_norm: bad sizes");
+    LGML_REQUIRE(out_dtype == LGML_F32 || out_dtype == LGML_BF16, "dyt_norm: unknown output type %d", out_dtype);
+    LGML_REQUIRE(delta == nullptr || n_parts >= 1, "dyt_norm: a delta has at least one part");
+    LGML_REQUIRE(delta == nullptr || delta_dtype == LGML_F32 || delta_dtype == LGML_BF16, "dyt_norm: unknown delta type %d", delta_dtype);
+    if (n_rows == 0) return 0;
+    rms::Args a;
+    a.x = x, a.delta = delta, a.n_parts = n_parts, a.part_stride = part_stride, a.delta_bias = delta_bias, a.weight = weight;
+    a.rows = rows, a.out = out, a.width = width, a.eps = 0.f, a.cs = 1;
+    const uintptr_t ptrs = (uintptr_t)x | (uintptr_t)delta | (uintptr_t)delta_bias | (uintptr_t)weight | (uintptr_t)shift | (uintptr_t)out;
+    a.vec = (width % 4 == 0 && part_stride % 4 == 0 && (ptrs & 15) == 0) ? 1 : 0;
+    if (delta != nullptr && delta_dtype == LGML_BF16)
+        return dyt_dispatch<__nv_bfloat16>(a, (const __nv_bfloat16 *)nullptr, shift, alpha, pre, out_dtype, n_rows, stream);
+    return dyt_dispatch<float>(a, (const float *)nullptr, shift, alpha, pre, out_dtype, n_rows, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// The clamped gated activation of a dense feed-forward:
+//   g = min(gate, limit), u = clamp(up, -limit, limit), act = g * sigmoid(alpha * g) * (u + 1)
+// gate and up as for silu_mul (two halves of a row, or neighbours when paired)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void glu_clamped_kernel(const T *__restrict__ gu, T *__restrict__ act, int n_tokens, int width, int paired, float alpha, float limit) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t total = (size_t)n_tokens * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / width, f = i - t * width;
+        const float g = fminf(to_f32(act_load(gu + t * 2 * width + (paired ? 2 * f : f))), limit);
+        const float u = fminf(fmaxf(to_f32(act_load(gu + t * 2 * width + (paired ? 2 * f + 1 : width + f))), -limit), limit);
+        act[i] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    }
+}
+
+LGML_API int lgml_glu_clamped(const void *gu, void *act, int dtype, int n_tokens, int width, int paired, float alpha, float limit,
+                              cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && width > 0, "glu_clamped: bad sizes");
+    if (n_tokens == 0) return 0;
+    const size_t total = (size_t)n_tokens * width;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == LGML_F32)
+        lgml_launch(glu_clamped_kernel<float>, blocks, threads, 0, stream, (const float *)gu, (float *)act, n_tokens, width, paired, alpha, limit);
+    else if (dtype == LGML_BF16)
+        lgml_launch(glu_clamped_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (const __nv_bfloat16 *)gu, (__nv_bfloat16 *)act, n_tokens,
+                    width, paired, alpha, limit);
+    else
+        LGML_FAIL("glu_clamped: unknown type %d", dtype);
+    return lgml_launch_status("glu_clamped");
 }
 
 // ---------------------------------------------------------------------------------------

@@ -12,23 +12,6 @@ LGML_DEFINE_LAST_ERROR(lgml_rope_cache)
 namespace {
 constexpr int ITEMS = 256;   // work items (pairs of elements) per block
 
-// sin and cos of pos * (f + f_lo).  The product of a position in the thousands and a float32
-// frequency is thousands of radians, and rounding it to float32 would cost 1e-4 to 1e-3 of a
-// radian there.  So: the rounded product a, its exact error (one fma), the frequency's low
-// part (what float32 lost of the float64 table; 0 when the caller has none), and a taken
-// modulo 2 pi exactly (2 pi in three float32 pieces; the first difference is exact for
-// positions below 2^24) before the small terms are added.  All of it float32 operations.
-__device__ __forceinline__ void rope_sincos(int pos, float f, float f_lo, float *s, float *c) {
-    const float p = (float)pos;
-    const float a = __fmul_rn(p, f);
-    const float e = fmaf(p, f_lo, fmaf(p, f, -a));
-    const float k = rintf(a * 0x1.45f306p-3f);
-    float r = fmaf(-k, 0x1.921fb6p+2f, a);
-    r = fmaf(-k, -0x1.777a5cp-23f, r);
-    r = fmaf(-k, -0x1.ee59dap-48f, r);
-    sincosf(r + e, s, c);
-}
-
 // One work item = one pair of elements of one head of one token.
 //   heads 0 .. H-1: q, rotated, written to q_out;   H .. H+Hkv-1: k, rotated, to the cache;
 //   H+Hkv .. H+2Hkv-1: v, copied to the cache.

@@ -108,9 +108,16 @@ class Runtime:
                                            out, n_heads, scale, window, self.status, softcap=softcap)
         return ops.paged_attention(q, batch, cache, out, n_heads, scale, window, self.status)
 
-    def sink_attention(self, q, batch, cache, out, n_heads: int, scale: float, window: int, slopes, sinks, gate) -> torch.Tensor:
-        """Attention with a sink, distance slopes, a window and an output gate (keys and values
-        with head sizes of their own) of the step's queries over the cache."""
+    def sink_attention(self, q, batch, cache, out, n_heads: int, scale: float, window: int, slopes, sinks, gate, keep_first: int = 0) -> torch.Tensor:
+        """Attention with a sink, distance slopes, a window (beyond which a request's first
+        ``keep_first`` tokens stay visible) and an output gate, of the step's queries over the
+        cache.  Keys and values have head sizes of their own; the values may have fewer heads
+        than the keys, or be the first entries of the key cells."""
+        plain = (not keep_first and cache.v.shape[1] == cache.k.shape[1] and cache.v.is_contiguous() and out.dtype == q.dtype)
+        if not plain:
+            # the general form knows every option
+            return ops.sink_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
+                                      window, self.status, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first)
         if (self.dtype == torch.bfloat16 and self.attention_backend != "ref" and batch.max_q_len > ops.DECODE_MAX_Q
                 and cache.k.shape[2] == 64 and cache.k.shape[3] <= 128 and cache.v.shape[3] <= 128):
             if ops.sink_twin_supports(q, out, cache.k, cache.v, gate):
@@ -132,6 +139,11 @@ class Runtime:
                                    self.status, n_splits, slopes=slopes, sinks=sinks, gate=gate)
         return ops.sink_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
                                   window, self.status, slopes=slopes, sinks=sinks, gate=gate)
+
+    # ---- mixture of experts ------------------------------------------------------------
+    def moe_experts(self, h, ids, wts, w_gate, w_up, w_down) -> torch.Tensor:
+        """The chosen experts' weighted outputs, float32 [tokens, width]."""
+        return ops.moe_experts_rows(h, ids, wts, w_gate, w_up, w_down)
 
     # ---- faults ------------------------------------------------------------------------
     def check_status(self, code: Optional[int] = None) -> None:

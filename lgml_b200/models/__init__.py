@@ -3,6 +3,7 @@ from ..config import lookup_architecture
 from .decoder import DecoderModel, LayerCall
 from . import llama  # noqa: F401  (registers LlamaForCausalLM)
 from . import lefulorn  # noqa: F401  (registers Lefulorn)
+from . import gotulorn  # noqa: F401  (registers Gotulorn)
 
 
 def build_model(config):

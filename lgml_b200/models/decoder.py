@@ -32,7 +32,7 @@ class DecoderModel:
     def __init__(self, config, embedding, blocks, final_norm, head, schedule: Optional[List[LayerCall]] = None,
                  block_prefix: str = "model.layers.{}", final_norm_prefix: str = "model.norm",
                  embed_scale: Optional[float] = None, logit_scale: Optional[float] = None, logit_softcap: Optional[float] = None,
-                 ignored_tensors: Sequence[str] = ()):
+                 ignored_tensors: Sequence[str] = (), embed_norm=None, embed_norm_prefix: str = "model.embed_norm"):
         self.config = config
         self.embedding = embedding
         self.blocks = list(blocks)
@@ -40,6 +40,8 @@ class DecoderModel:
         self.head = head
         self.block_prefix = block_prefix
         self.final_norm_prefix = final_norm_prefix
+        # a norm between the embedding and the first layer (None: the rows themselves are the residual stream)
+        self.embed_norm, self.embed_norm_prefix = embed_norm, embed_norm_prefix
         # name patterns of tensors that a folder of this architecture may carry unread
         self.ignored_tensors = tuple(ignored_tensors)
         # scales that other families of the reference apply and Llama does not (None = no kernel):
@@ -56,13 +58,15 @@ class DecoderModel:
                 if self.schedule[call.cache].cache is not None:
                     raise ValueError(f"schedule entry {ci} reads the cache of entry {call.cache}, which has none of its own")
         self.vocab_size = head.vocab
-        parts = [embedding, final_norm, head] + self.blocks
+        parts = [embedding, final_norm, head] + self.blocks + ([embed_norm] if embed_norm is not None else [])
         self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
         self.max_position = getattr(config, "max_position_embeddings", None)
 
     # ---- weights -----------------------------------------------------------------------
     def tensor_specs(self) -> List[TensorSpec]:
         specs = list(self.embedding.tensor_specs(""))
+        if self.embed_norm is not None:
+            specs += self.embed_norm.tensor_specs(self.embed_norm_prefix)
         for i, b in enumerate(self.blocks):
             specs += b.tensor_specs(self.block_prefix.format(i))
         specs += self.final_norm.tensor_specs(self.final_norm_prefix)
@@ -74,6 +78,8 @@ class DecoderModel:
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt) -> None:
         self.embedding.bind("", tensors, rt)
+        if self.embed_norm is not None:
+            self.embed_norm.bind(self.embed_norm_prefix, tensors, rt)
         for i, b in enumerate(self.blocks):
             b.bind(self.block_prefix.format(i), tensors, rt)
         self.final_norm.bind(self.final_norm_prefix, tensors, rt)
@@ -96,6 +102,8 @@ class DecoderModel:
         x = self.embedding.forward(rt, batch.token_ids)
         if self.embed_scale is not None:
             ops.scale_cap(x, self.embed_scale)
+        if self.embed_norm is not None:
+            x = self.embed_norm.forward(rt, x, torch.float32)
         pending = None
         for ci, call in enumerate(self.schedule):
             owner = ci if call.cache is None else call.cache

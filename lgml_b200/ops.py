@@ -238,6 +238,58 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     return out
 
 
+def dyt_norm(x: torch.Tensor, weight: torch.Tensor, shift: torch.Tensor, alpha: torch.Tensor, out: torch.Tensor, delta=None,
+             rows: Optional[torch.Tensor] = None, pre_scale: float = 1.0) -> torch.Tensor:
+    """out = tanh(alpha * pre_scale * (x [+ delta])) * weight + shift (a norm without mean or variance);
+    ``alpha`` is one float32 on the device.  ``delta`` and ``rows`` as for ``rmsnorm``."""
+    _need(x, "norm input", torch.float32, 2)
+    _need(weight, "norm weight", torch.float32, 1)
+    _need(shift, "norm shift", torch.float32, 1)
+    _need(alpha, "norm alpha", torch.float32)
+    _need(out, "norm output", ndim=2)
+    width = x.shape[1]
+    n_rows = out.shape[0]
+    if not x.is_contiguous() or not out.is_contiguous() or out.shape[1] != width or weight.numel() != width or shift.numel() != width or alpha.numel() != 1:
+        raise KernelError(f"dyt_norm: shapes disagree: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if rows is None and n_rows != x.shape[0]:
+        raise KernelError("dyt_norm: without a row list the output has the input's rows")
+    if rows is not None:
+        _need(rows, "row list", torch.int32, 1)
+        if rows.numel() != n_rows:
+            raise KernelError("dyt_norm: one output row per listed row")
+    ddt, n_parts, stride, dbias, dptr = F32, 1, 0, None, None
+    if isinstance(delta, Partials):
+        d = delta.data
+        _need(d, "residual delta parts", torch.float32, 3)
+        if tuple(d.shape[1:]) != tuple(x.shape) or not d.is_contiguous():
+            raise KernelError("dyt_norm: delta parts must be [parts, rows, width] and contiguous")
+        n_parts, stride, dbias, dptr = d.shape[0], d.shape[1] * d.shape[2], delta.bias, d
+    elif delta is not None:
+        _need(delta, "residual delta", ndim=2)
+        if delta.shape != x.shape or not delta.is_contiguous():
+            raise KernelError("dyt_norm: delta must have the input's shape and be contiguous")
+        ddt, dptr = dtype_code(delta.dtype), delta
+    fn = _fn("elementwise", "lgml_dyt_norm", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+                                              c_void_p, c_int, c_int, c_int, c_void_p])
+    _check("elementwise", fn(_ptr(x), _ptr(dptr), ddt, n_parts, stride, _ptr(dbias), _ptr(weight), _ptr(shift), _ptr(alpha), float(pre_scale),
+                             _ptr(rows), _ptr(out), dtype_code(out.dtype), n_rows, width, _stream()), "dyt_norm")
+    return out
+
+
+def glu_clamped(gate_up: torch.Tensor, out: torch.Tensor, alpha: float, limit: float, paired: bool = False) -> torch.Tensor:
+    """out[t, f] = g * sigmoid(alpha g) * (u + 1) with g = min(gate[t, f], limit), u = clamp(up[t, f], -limit, limit);
+    gate|up laid out as for ``silu_mul``."""
+    _need(gate_up, "gate|up", ndim=2)
+    _need(out, "activation", gate_up.dtype, 2)
+    n, two_f = gate_up.shape
+    if two_f != 2 * out.shape[1] or out.shape[0] != n or not gate_up.is_contiguous() or not out.is_contiguous():
+        raise KernelError(f"glu_clamped: shapes disagree: gate|up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
+    fn = _fn("elementwise", "lgml_glu_clamped", [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    _check("elementwise", fn(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), n, out.shape[1], 1 if paired else 0, float(alpha), float(limit),
+                             _stream()), "glu_clamped")
+    return out
+
+
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, paired: bool = False) -> torch.Tensor:
     """out[t, f] = silu(gate[t, f]) * up[t, f]; gate|up are the two halves of a row, or, with
     ``paired``, neighbours (gate at 2f, up at 2f + 1)."""
@@ -432,7 +484,8 @@ def sink_qkv_store(proj: torch.Tensor, positions: torch.Tensor, seq_of_token: to
                    v_lambda: Optional[torch.Tensor] = None, write_kv: bool = True) -> torch.Tensor:
     """From the fused projection's float32 output ``proj`` [tokens, q | k | v | ...]: q times its
     position's temperature 1 + coef ln(floor((p + 1) / every) + 1) into a buffer of the cache's
-    type (returned, [tokens, H D]); k and v into their cells.  ``v_mode`` 1 also keeps v in
+    type (returned, [tokens, H D]); k and v into their cells (the value pages may have fewer heads
+    than the key pages: several key heads then share a value head).  ``v_mode`` 1 also keeps v in
     ``v_keep`` (float32 [tokens, Hkv Dv]); 2 stores (1 - lambda) v + lambda v_keep instead of v."""
     _need(proj, "projection output", torch.float32, 2)
     _need(k_pages, "key pages", ndim=4)
@@ -440,10 +493,10 @@ def sink_qkv_store(proj: torch.Tensor, positions: torch.Tensor, seq_of_token: to
     ldp = _rows_contiguous(proj, "projection output")
     n = proj.shape[0]
     n_pages, hkv, page, d = k_pages.shape
-    dv = v_pages.shape[3]
-    if v_pages.shape[:3] != k_pages.shape[:3] or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+    hv, dv = v_pages.shape[1], v_pages.shape[3]
+    if (v_pages.shape[0], v_pages.shape[2]) != (n_pages, page) or hkv % hv or not k_pages.is_contiguous() or not v_pages.is_contiguous():
         raise KernelError(f"sink_qkv_store: key pages {tuple(k_pages.shape)} and value pages {tuple(v_pages.shape)} do not go together")
-    if proj.shape[1] < n_heads * d + hkv * (d + dv):
+    if proj.shape[1] < n_heads * d + (hkv * d + hv * dv if write_kv else 0):
         raise KernelError(f"sink_qkv_store: {proj.shape[1]} columns do not hold q, k and v")
     _need(positions, "positions", torch.int32, 1)
     _need(seq_of_token, "request index of tokens", torch.int32, 1)
@@ -452,43 +505,58 @@ def sink_qkv_store(proj: torch.Tensor, positions: torch.Tensor, seq_of_token: to
         raise KernelError("sink_qkv_store: one position and one request index per token, and a contiguous block table")
     if v_mode:
         _need(v_keep, "kept values", torch.float32, 2)
-        if tuple(v_keep.shape) != (n, hkv * dv) or not v_keep.is_contiguous():
-            raise KernelError(f"sink_qkv_store: kept values must be a contiguous [{n}, {hkv * dv}]")
+        if tuple(v_keep.shape) != (n, hv * dv) or not v_keep.is_contiguous():
+            raise KernelError(f"sink_qkv_store: kept values must be a contiguous [{n}, {hv * dv}]")
     if v_mode == 2:
         _need(v_lambda, "mixing weight", torch.float32)
     q_out = torch.empty((n, n_heads * d), dtype=k_pages.dtype, device=proj.device)
     fn = _fn("attention_sink", "lgml_sink_qkv_store", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
                                                        c_void_p, c_int, c_void_p, c_void_p])
     _check("attention_sink", fn(_ptr(proj), ldp, _ptr(q_out), dtype_code(k_pages.dtype), q_out.stride(0), _ptr(positions), _ptr(seq_of_token),
-                                _ptr(block_table), block_table.shape[1], _ptr(k_pages), _ptr(v_pages), n_pages, page, n, n_heads, hkv, d, dv,
+                                _ptr(block_table), block_table.shape[1], _ptr(k_pages), _ptr(v_pages), n_pages, page, n, n_heads, hkv, hv, d, dv,
                                 float(temp_coef), int(temp_every), int(v_mode), _ptr(v_keep), _ptr(v_lambda), 1 if write_kv else 0,
                                 _ptr(status), _stream()), "sink_qkv_store")
     return q_out
 
 
+def _value_pages(v_pages: torch.Tensor, k_pages: torch.Tensor, who: str):
+    """(value heads, value size, elements between value rows) of value pages that are their own tensor
+    or a column range of wider cells (the first columns of the key cells, say)."""
+    n_pages, hkv, page, _ = k_pages.shape
+    hv, dv = v_pages.shape[1], v_pages.shape[3]
+    ldv = v_pages.stride(2)
+    if (v_pages.shape[0], v_pages.shape[2]) != (n_pages, page) or hkv % hv or v_pages.stride(3) != 1 or ldv < dv \
+            or v_pages.stride(1) != page * ldv or v_pages.stride(0) != hv * page * ldv:
+        raise KernelError(f"{who}: value pages {tuple(v_pages.shape)} (strides {v_pages.stride()}) do not go with key pages {tuple(k_pages.shape)}")
+    return hv, dv, ldv
+
+
 def sink_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                    k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
                    status: torch.Tensor, slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
-                   gate: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t, h] = sum_j w_j v_j over the request's keys at positions p - window < j <= p (all j <= p
-    when window is 0), w_j = exp(s_j) / (exp(sink_h) + sum exp(s)), s_j = (q . k_j) scale - slope_h (p - j);
+                   gate: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
+    """out[t, h] = sum_j w_j v_j over the request's keys at positions j <= p with p - j < window (all j <= p
+    when window is 0) or j < ``keep_first`` (the request's first tokens stay visible beyond the window),
+    w_j = exp(s_j) / (exp(sink_h) + sum exp(s)), s_j = (q . k_j) scale - slope_h (p - j);
     then times sigmoid(gate[t, h]) element by element when ``gate`` (float32, pre-sigmoid; may be a
-    column slice) is given.  Keys have head size D, values Dv."""
+    column slice) is given.  Keys have head size D, values Dv.  The value pages may have fewer heads than the
+    key pages (key heads g Hkv / Hv ... share value head g) and may be a column range of wider cells.
+    ``out`` has the queries' type or is float32."""
     _need(q, "queries", ndim=2)
-    _need(out, "attention output", q.dtype, 2)
+    _need(out, "attention output", ndim=2)
     ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
     n = q.shape[0]
     _need(k_pages, "key pages", q.dtype, 4)
     _need(v_pages, "value pages", q.dtype, 4)
     n_pages, hkv, page, d = k_pages.shape
-    dv = v_pages.shape[3]
+    hv, dv, ldv = _value_pages(v_pages, k_pages, "sink_attention")
     _need(positions, "positions", torch.int32, 1)
     _need(seq_of_token, "request index of tokens", torch.int32, 1)
     _need(block_table, "block table", torch.int32, 2)
-    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * dv):
-        raise KernelError(f"sink_attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {n_heads} heads of {d} and {dv}")
-    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
+    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * dv) or out.dtype not in (q.dtype, torch.float32):
+        raise KernelError(f"sink_attention: q {tuple(q.shape)} / out {tuple(out.shape)} {out.dtype} do not fit {n_heads} heads of {d} and {dv}")
+    if not k_pages.is_contiguous() or not block_table.is_contiguous():
         raise KernelError("sink_attention: pages and block table must be contiguous")
     for t, what in ((slopes, "slopes"), (sinks, "sinks")):
         if t is not None:
@@ -502,11 +570,12 @@ def sink_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch
         if tuple(gate.shape) != (n, n_heads * dv):
             raise KernelError(f"sink_attention: gate {tuple(gate.shape)} is not [{n}, {n_heads * dv}]")
     fn = _fn("attention_sink", "lgml_sink_attention", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-                                                       c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                       c_float, c_int, c_void_p, c_void_p])
+                                                       c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                       c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
     _check("attention_sink", fn(_ptr(q), dtype_code(q.dtype), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1],
-                                _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), ldo, n, n_heads,
-                                hkv, d, dv, float(scale), int(window or 0), _ptr(status), _stream()), "sink_attention")
+                                _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out),
+                                dtype_code(out.dtype), ldo, n, n_heads, hkv, hv, d, dv, ldv, float(scale), int(window or 0), int(keep_first or 0),
+                                _ptr(status), _stream()), "sink_attention")
     return out
 
 
@@ -654,6 +723,139 @@ def sink_decode(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Te
     _check("attention_sink", fn(_ptr(q), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(k_pages),
                                 _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), ldo, _ptr(scratch),
                                 int(n_splits), n, n_heads, hkv, d, dv, float(scale), int(window or 0), _ptr(status), _stream()), "sink_decode")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# per head, around attention: differential maps, latent keys and values
+# ----------------------------------------------------------------------------------------
+
+def diff_combine(maps: torch.Tensor, out: torch.Tensor, n_heads: int, n_key_heads: int, lam: float, eps: float, out_scale: float) -> torch.Tensor:
+    """Differential attention's combination: ``maps`` [tokens, 2 H Dv] holds two attention outputs per
+    head, in the order (key head g, map m, head r of the group); out[t, h] = o / sqrt(mean(o^2) + eps) *
+    out_scale with o = a1 - lam a2."""
+    _need(maps, "attention maps", ndim=2)
+    _need(out, "combined output", ndim=2)
+    ldi, ldo = _rows_contiguous(maps, "attention maps"), _rows_contiguous(out, "combined output")
+    n = maps.shape[0]
+    if maps.shape[1] % (2 * n_heads) or out.shape != (n, maps.shape[1] // 2) or n_heads % n_key_heads:
+        raise KernelError(f"diff_combine: maps {tuple(maps.shape)} / out {tuple(out.shape)} do not fit {n_heads} heads on {n_key_heads}")
+    dv = maps.shape[1] // (2 * n_heads)
+    fn = _fn("attention_heads", "lgml_diff_combine", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                                      c_float, c_void_p])
+    _check("attention_heads", fn(_ptr(maps), dtype_code(maps.dtype), ldi, _ptr(out), dtype_code(out.dtype), ldo, n, n_heads, n_key_heads, dv,
+                                 float(lam), float(eps), float(out_scale), _stream()), "diff_combine")
+    return out
+
+
+def latent_prepare(q_proj: torch.Tensor, down: torch.Tensor, norm_w: torch.Tensor, eps: float, inv_freq: torch.Tensor, n_rot: int,
+                   positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, cells: torch.Tensor, n_heads: int,
+                   head_dim: int, rot_dim: int, rank: int, status: torch.Tensor, write_kv: bool = True):
+    """Latent attention between its projections and attention.  ``q_proj`` float32 [tokens, H (D + Dr)]
+    (per head D plain, then Dr rotated entries), ``down`` float32 [tokens, R + Dr].  The first R columns
+    of ``down``, over their root mean square, times ``norm_w``, are the latent c; the last Dr are a key
+    part that is rotated (the first ``n_rot`` entries, pairs (2i, 2i + 1), ``inv_freq`` [2, n_rot / 2]:
+    the float32 frequencies and what float32 lost of them).  [c | rotated part] goes into the token's
+    cell of ``cells`` [pages, 1, page, R + Dr].  Returns (q_plain [tokens, H D], q_full [tokens,
+    H (R + Dr)]) in the cells' type; of q_full only the rotated Dr entries behind each head's first R
+    are written (``head_linear`` fills those)."""
+    _need(q_proj, "query projection", torch.float32, 2)
+    _need(down, "down projection", torch.float32, 2)
+    _need(cells, "latent cells", ndim=4)
+    _need(norm_w, "latent norm weight", torch.float32, 1)
+    _need(inv_freq, "frequencies", torch.float32, 2)
+    n = q_proj.shape[0]
+    n_pages, one, page, width = cells.shape
+    if one != 1 or width != rank + rot_dim or not cells.is_contiguous():
+        raise KernelError(f"latent_prepare: cells {tuple(cells.shape)} are not [pages, 1, page, {rank + rot_dim}]")
+    if q_proj.shape[1] != n_heads * (head_dim + rot_dim) or tuple(down.shape) != (n, rank + rot_dim) or norm_w.numel() != rank:
+        raise KernelError(f"latent_prepare: q {tuple(q_proj.shape)} / down {tuple(down.shape)} do not fit {n_heads} heads of {head_dim} + {rot_dim}, rank {rank}")
+    if n_rot % 2 or n_rot > rot_dim or tuple(inv_freq.shape) != (2, max(n_rot // 2, 1)) or not inv_freq.is_contiguous():
+        raise KernelError(f"latent_prepare: {n_rot} rotated entries of {rot_dim}, frequencies {tuple(inv_freq.shape)}")
+    _need(positions, "positions", torch.int32, 1)
+    _need(seq_of_token, "request index of tokens", torch.int32, 1)
+    _need(block_table, "block table", torch.int32, 2)
+    if positions.numel() != n or seq_of_token.numel() != n or not block_table.is_contiguous():
+        raise KernelError("latent_prepare: one position and one request index per token, and a contiguous block table")
+    ldq, ldd = _rows_contiguous(q_proj, "query projection"), _rows_contiguous(down, "down projection")
+    q_plain = torch.empty((n, n_heads * head_dim), dtype=cells.dtype, device=cells.device)
+    q_full = torch.empty((n, n_heads * (rank + rot_dim)), dtype=cells.dtype, device=cells.device)
+    fn = _fn("attention_heads", "lgml_latent_prepare", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p,
+                                                        c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
+                                                        c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check("attention_heads", fn(_ptr(q_proj), ldq, _ptr(down), ldd, _ptr(norm_w), float(eps), _ptr(inv_freq[0]), _ptr(inv_freq[1]), int(n_rot),
+                                 _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(cells), dtype_code(cells.dtype),
+                                 n_pages, page, _ptr(q_plain), q_plain.stride(0), _ptr(q_full), q_full.stride(0), n, n_heads, head_dim, rot_dim,
+                                 rank, 1 if write_kv else 0, _ptr(status), _stream()), "latent_prepare")
+    return q_plain, q_full
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head_stride: int, out_head_stride: int) -> torch.Tensor:
+    """A product per head: out[t, h * out_head_stride + o] = sum_k x[t, h * x_head_stride + k] w[h, o, k];
+    ``w`` [H, O, K] contiguous, x and out 2-D with dense rows, all of one type (float32 sums)."""
+    _need(x, "head_linear input", ndim=2)
+    _need(w, "head_linear weights", x.dtype, 3)
+    _need(out, "head_linear output", x.dtype, 2)
+    ldx, ldo = _rows_contiguous(x, "head_linear input"), _rows_contiguous(out, "head_linear output")
+    H, O, K = w.shape
+    n = x.shape[0]
+    if not w.is_contiguous() or out.shape[0] != n or (H - 1) * x_head_stride + K > x.shape[1] or (H - 1) * out_head_stride + O > out.shape[1]:
+        raise KernelError(f"head_linear: x {tuple(x.shape)} / w {tuple(w.shape)} / out {tuple(out.shape)} with head strides {x_head_stride}, {out_head_stride} do not fit")
+    fn = _fn("attention_heads", "lgml_head_linear", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check("attention_heads", fn(_ptr(x), ldx, int(x_head_stride), _ptr(w), _ptr(out), ldo, int(out_head_stride), dtype_code(x.dtype), n, H, O, K,
+                                 _stream()), "head_linear")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# mixture of experts
+# ----------------------------------------------------------------------------------------
+
+def moe_router(h: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor], top: int):
+    """The ``top`` experts with the largest float32 logits W_r h + b_r per token (ties: the lower index)
+    and the softmax over those logits alone: (ids int32 [tokens, top], weights float32 [tokens, top])."""
+    _need(h, "router input", ndim=2)
+    _need(w_router, "router weight", torch.float32, 2)
+    ldh = _rows_contiguous(h, "router input")
+    n, E = h.shape
+    X = w_router.shape[0]
+    if w_router.shape[1] != E or not w_router.is_contiguous() or not 0 < top <= X:
+        raise KernelError(f"moe_router: weight {tuple(w_router.shape)} does not fit rows of {E}, or {top} of {X} experts")
+    if b_router is not None:
+        _need(b_router, "router bias", torch.float32, 1)
+        if b_router.numel() != X:
+            raise KernelError("moe_router: one bias per expert")
+    ids = torch.empty((n, top), dtype=torch.int32, device=h.device)
+    wts = torch.empty((n, top), dtype=torch.float32, device=h.device)
+    fn = _fn("moe", "lgml_moe_router", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check("moe", fn(_ptr(h), dtype_code(h.dtype), ldh, _ptr(w_router), _ptr(b_router), _ptr(ids), _ptr(wts), n, E, X, int(top), _stream()), "moe_router")
+    return ids, wts
+
+
+def moe_experts_rows(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_s wts[t, s] W_down[e] (silu(W_gate[e] h_t) * (W_up[e] h_t)), e = ids[t, s]: float32
+    [tokens, E].  The experts' matrices stacked: gate and up [X, F, E], down [X, E, F].  A block per
+    (token, chosen expert): the form for few tokens and for the 32-bit path."""
+    _need(h, "experts' input", ndim=2)
+    for t, what in ((w_gate, "gate"), (w_up, "up"), (w_down, "down")):
+        _need(t, f"experts' {what} matrices", h.dtype, 3)
+        if not t.is_contiguous():
+            raise KernelError(f"moe_experts_rows: the {what} matrices must be contiguous")
+    _need(ids, "chosen experts", torch.int32, 2)
+    _need(wts, "experts' weights", torch.float32, 2)
+    ldh = _rows_contiguous(h, "experts' input")
+    n, E = h.shape
+    X, F, _ = w_gate.shape
+    top = ids.shape[1]
+    if tuple(w_gate.shape) != (X, F, E) or tuple(w_up.shape) != (X, F, E) or tuple(w_down.shape) != (X, E, F) or tuple(ids.shape) != (n, top) \
+            or tuple(wts.shape) != (n, top) or not ids.is_contiguous() or not wts.is_contiguous():
+        raise KernelError(f"moe_experts_rows: shapes disagree: h {tuple(h.shape)}, gate {tuple(w_gate.shape)}, down {tuple(w_down.shape)}, ids {tuple(ids.shape)}")
+    act = torch.empty((n * top, F), dtype=h.dtype, device=h.device)
+    out = torch.empty((n, E), dtype=torch.float32, device=h.device)
+    fn = _fn("moe", "lgml_moe_experts_rows", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                              c_int, c_int, c_int, c_void_p])
+    _check("moe", fn(_ptr(h), dtype_code(h.dtype), ldh, _ptr(ids), _ptr(wts), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _ptr(act), _ptr(out), n, E, F, X,
+                     top, _stream()), "moe_experts_rows")
     return out
 
 
@@ -977,6 +1179,9 @@ def gemm_bf16_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, bias_pairs: Optiona
     if x.shape[0] == 0:
         return out
     return gemm_tcgen05(x, w_pairs, out, bias_pairs, status, swiglu=True)
+
+
+GLU_CLAMPED_FUSED = False     # the clamped gated activation in the product's epilogue (not built: the two-kernel form runs)
 
 
 def gemm_bf16_relu_sq(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], status: torch.Tensor) -> torch.Tensor:

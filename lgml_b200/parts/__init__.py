@@ -3,10 +3,13 @@ from .base import KINDS, Part, make_part, register_part, registered
 from .block import PreNormBlock
 from .embedding import LMHead, TokenEmbedding
 from .delta import ChannelDelta
-from .mlp import DenseMLP, GatedMLP
-from .norm import RMSNorm
+from .diff_attention import DifferentialAttention
+from .latent_attention import LatentAttention
+from .moe import RoutedExperts
+from .mlp import ClampedGLU, DenseMLP, GatedMLP
+from .norm import DynamicTanh, RMSNorm
 from .sink_attention import SinkAttention
 from .rope import NoPosition, Rope, RotaryPosition, frequency_factors, store_kv
 
 __all__ = ["Attention", "KINDS", "Part", "make_part", "register_part", "registered", "PreNormBlock", "LMHead",
-           "TokenEmbedding", "GatedMLP", "DenseMLP", "ChannelDelta", "SinkAttention", "RMSNorm", "NoPosition", "Rope", "RotaryPosition", "frequency_factors", "store_kv"]
+           "TokenEmbedding", "GatedMLP", "DenseMLP", "ClampedGLU", "RoutedExperts", "ChannelDelta", "SinkAttention", "DifferentialAttention", "LatentAttention", "RMSNorm", "DynamicTanh", "NoPosition", "Rope", "RotaryPosition", "frequency_factors", "store_kv"]

@@ -92,5 +92,45 @@ class DenseMLP(Part):
         return rt.linear(act, self.wd, bias=self.bd, partials_ok=True)
 
 
+class ClampedGLU(Part):
+    """The gated feed-forward with clamped branches: g = min(W_gate h, limit), u = clamp(W_up h,
+    -limit, limit), y = W_down (g * sigmoid(alpha g) * (u + 1)).  Gate and up are one product."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, inner: int, limit: float, alpha: float = 1.702):
+        self.width, self.inner, self.limit, self.alpha = width, inner, float(limit), float(alpha)
+        self.wgu = self.wd = None
+        self.paired = False
+
+    def tensor_specs(self, prefix):
+        E, F = self.width, self.inner
+        return [TensorSpec(prefix + ".gate", (F, E)), TensorSpec(prefix + ".up", (F, E)), TensorSpec(prefix + ".down", (E, F))]
+
+    def bind(self, prefix, tensors, rt):
+        wg, wu = tensors[prefix + ".gate"], tensors[prefix + ".up"]
+        self.wd = tensors[prefix + ".down"]
+        # bfloat16: the gate and up rows of a feature lie next to each other, so that the product's
+        # epilogue has both and applies the activation itself; float32: gate rows, then up rows
+        self.paired = rt.dtype == torch.bfloat16
+        if self.paired:
+            self.wgu = torch.stack([wg, wu], dim=1).reshape(2 * self.inner, self.width).contiguous()
+        else:
+            self.wgu = torch.cat([wg, wu], dim=0).contiguous()
+
+    def first_weights(self):
+        return [self.wgu]
+
+    def forward(self, rt, h):
+        if self.paired and rt.fused_swiglu(h, self.wgu) and ops.GLU_CLAMPED_FUSED:
+            act = ops.gemm_bf16_glu_clamped(h, self.wgu, self.alpha, self.limit, rt.status)
+        else:
+            gu = rt.linear(h, self.wgu)
+            act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
+            ops.glu_clamped(gu, act, self.alpha, self.limit, paired=self.paired)
+        return rt.linear(act, self.wd, partials_ok=True)
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "clamped_glu", ClampedGLU)
 register_part("feed_forward", "dense_mlp", DenseMLP)

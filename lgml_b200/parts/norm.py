@@ -1,6 +1,6 @@
-"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * w, in float32
+"""Norm parts.  RMSNorm: y = x / sqrt(mean(x^2) + eps) * w, in float32
 (``src/lgml.c:1626-1633``; the weight is the separate multiply of
-``lua/lgml/transformer.lua:1760``, ``:2044``, ``:2095``)."""
+``lua/lgml/transformer.lua:1760``, ``:2044``, ``:2095``).  DynamicTanh: y = tanh(alpha x) * w + b."""
 from __future__ import annotations
 
 import torch
@@ -32,4 +32,32 @@ class RMSNorm(Part):
         return ops.rmsnorm(x, self.weight, self.eps, out, delta=delta, rows=rows)
 
 
+class DynamicTanh(Part):
+    """Dynamic tanh: y = tanh(alpha x) * w + b, element by element, with a learned scalar alpha: a
+    norm that computes no mean and no variance.  Tensors: the weight under the part's prefix itself,
+    ``.b`` and ``.alpha`` beside it.  ``pre_scale`` multiplies x first (a norm that follows a scaled
+    embedding takes the scale with it and the scaled rows are never written)."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, pre_scale: float = 1.0):
+        self.width = width
+        self.pre_scale = float(pre_scale)
+        self.weight = self.shift = self.alpha = None
+
+    def tensor_specs(self, prefix):
+        return [TensorSpec(prefix, (self.width,), VECTOR, init=(1.0, 1.0)), TensorSpec(prefix + ".b", (self.width,), VECTOR),
+                TensorSpec(prefix + ".alpha", (), VECTOR, init=(0.5, 1.0))]
+
+    def bind(self, prefix, tensors, rt):
+        self.weight, self.shift = tensors[prefix], tensors[prefix + ".b"]
+        self.alpha = tensors[prefix + ".alpha"].reshape(1).contiguous()
+
+    def forward(self, rt, x, out_dtype, delta=None, rows=None):
+        n = x.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.width), dtype=out_dtype, device=x.device)
+        return ops.dyt_norm(x, self.weight, self.shift, self.alpha, out, delta=delta, rows=rows, pre_scale=self.pre_scale)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "dynamic_tanh", DynamicTanh)
