@@ -189,6 +189,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// a result as bfloat16, or as float32 for a caller that combines heads afterwards
+__device__ __forceinline__ void store_out(void *out, int out_f32, size_t idx, float v) {
+    if (out_f32) reinterpret_cast<float *>(out)[idx] = v;
+    else reinterpret_cast<__nv_bfloat16 *>(out)[idx] = __float2bfloat16_rn(v);
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t *>(&v);
@@ -222,8 +227,8 @@ __global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
     const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ tiles,
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, const float *__restrict__ slopes, const float *__restrict__ sinks,
-    const float *__restrict__ gate, int ldg, __nv_bfloat16 *__restrict__ out, int ldo, int H, int Hkv, int D, int Dv, float scale,
-    int window, int *__restrict__ status) {
+    const float *__restrict__ gate, int ldg, void *__restrict__ out, int out_f32, int ldo, int H, int Hkv, int Hv, int D, int Dv, int ldv,
+    float scale, int window, int keep_first, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
     constexpr int DP = KS * 16, DVP = NV * 8;
@@ -236,6 +241,7 @@ __global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
     __nv_bfloat16 *Vs = Ks + 2 * PAGE * LDK;
     const int tile = blockIdx.x, h = blockIdx.y;
     const int g = h / (H / Hkv);
+    const int gv = g / (Hkv / Hv);
     const int seq = tiles[tile * 4], row0 = tiles[tile * 4 + 1], n_tok = tiles[tile * 4 + 2];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int mat = lane >> 3, mrow = lane & 7;
@@ -264,13 +270,18 @@ __global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
 
     // With rows of whole 16-byte pieces the pages come by cp.async into two buffers in turn: the
     // copy of the next page runs under the products of this one.  Else one buffer, plain loads.
-    const bool pipelined = (D % 8 == 0) && (Dv % 8 == 0);
+    const bool pipelined = (D % 8 == 0) && (Dv % 8 == 0) && (ldv % 8 == 0) && ((reinterpret_cast<uintptr_t>(v_pages) & 15) == 0);
     const int pg_first = lo_key / PAGE, pg_last = p_last / PAGE;
+    // the pages walked: those of the kept first tokens that lie before the window's, then the window's
+    const int n_kp = window > 0 ? min((keep_first + PAGE - 1) / PAGE, pg_first) : 0;
+    const int n_iter = n_kp + pg_last - pg_first + 1;
+    auto page_at = [&](int it) { return it < n_kp ? it : pg_first + (it - n_kp); };
     auto issue = [&](int pg, int buf) {
         const int page = pg < max_blocks ? table[pg] : -1;
         const bool have = page >= 0 && page < n_pages;
         if (!have && threadIdx.x == 0) atomicExch(status, 3);
         const size_t cell0 = ((size_t)(have ? page : 0) * Hkv + g) * PAGE;
+        const size_t vcell0 = ((size_t)(have ? page : 0) * Hv + gv) * PAGE;
         __nv_bfloat16 *Kb = Ks + (size_t)buf * PAGE * LDK, *Vb = Vs + (size_t)buf * PAGE * LDV;
         for (int c = threadIdx.x; c < PAGE * (DP / 8); c += blockDim.x) {
             const int r = c / (DP / 8), col = (c - r * (DP / 8)) * 8;
@@ -282,19 +293,20 @@ __global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
             const int r = c / (DVP / 8), col = (c - r * (DVP / 8)) * 8;
             const int bytes = (have && col < Dv) ? 16 : 0;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(Vb + (size_t)r * LDV + col)),
-                         "l"(v_pages + (cell0 + r) * Dv + (col < Dv ? col : 0)), "r"(bytes) : "memory");
+                         "l"(v_pages + (vcell0 + r) * ldv + (col < Dv ? col : 0)), "r"(bytes) : "memory");
         }
     };
     if (pipelined) {
-        issue(pg_first, 0);
+        issue(page_at(0), 0);
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    for (int pg = pg_first; pg <= pg_last; ++pg) {
-        const int buf = pipelined ? ((pg - pg_first) & 1) : 0;
+    for (int it = 0; it < n_iter; ++it) {
+        const int pg = page_at(it);
+        const int buf = pipelined ? (it & 1) : 0;
         const __nv_bfloat16 *Kb = Ks + (size_t)buf * PAGE * LDK, *Vb = Vs + (size_t)buf * PAGE * LDV;
         __syncthreads();            // everyone is done with the page before: its buffer is free
         if (pipelined) {
-            if (pg < pg_last) issue(pg + 1, buf ^ 1);
+            if (it + 1 < n_iter) issue(page_at(it + 1), buf ^ 1);
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
@@ -302,14 +314,15 @@ __global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
             const bool have = page >= 0 && page < n_pages;
             if (!have && threadIdx.x == 0) atomicExch(status, 3);
             const size_t cell0 = ((size_t)(have ? page : 0) * Hkv + g) * PAGE;
+            const size_t vcell0 = ((size_t)(have ? page : 0) * Hv + gv) * PAGE;
             load_rows(Ks, LDK, PAGE, D, DP, false, [&](int r) { return have ? k_pages + (cell0 + r) * D : nullptr; });
-            load_rows(Vs, LDV, PAGE, Dv, DVP, false, [&](int r) { return have ? v_pages + (cell0 + r) * Dv : nullptr; });
+            load_rows(Vs, LDV, PAGE, Dv, DVP, false, [&](int r) { return have ? v_pages + (vcell0 + r) * ldv : nullptr; });
         }
         __syncthreads();
         // the warp's rows see keys up to their own positions: skip a page that lies wholly outside
         const int w_first = p0 + warp * 16, w_last = min(w_first + 15, p_last);
         const int key0 = pg * PAGE;
-        if (warp * 16 >= n_tok || key0 > w_last || (window > 0 && key0 + PAGE - 1 < w_first - window + 1)) continue;
+        if (warp * 16 >= n_tok || key0 > w_last || (window > 0 && key0 + PAGE - 1 < w_first - window + 1 && key0 >= keep_first)) continue;
 
         float sacc[8][4];
 #pragma unroll
@@ -348,7 +361,7 @@ __global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
                     const int rr = i >> 1;
                     const int j = key0 + nt * 8 + (lane & 3) * 2 + (i & 1);
                     const int dist = qpos[rr] - j;
-                    const bool ok = qok[rr] && dist >= 0 && (window == 0 || dist < window);
+                    const bool ok = qok[rr] && dist >= 0 && (window == 0 || dist < window || j < keep_first);
                     const float sv = ok ? sacc[nt][i] * scale2 - slope2 * (float)dist : -INFINITY;
                     sacc[nt][i] = sv;
                     mx[rr] = fmaxf(mx[rr], sv);
@@ -414,7 +427,7 @@ __global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
                 if (d >= Dv) continue;
                 float o = oacc[nv][rr * 2 + e] * inv;
                 if (gate) o *= 1.0f / (1.0f + __expf(-act_load(gate + t * ldg + (size_t)h * Dv + d)));
-                out[t * ldo + (size_t)h * Dv + d] = __float2bfloat16_rn(o);
+                store_out(out, out_f32, t * ldo + (size_t)h * Dv + d, o);
             }
     }
 }
@@ -422,14 +435,15 @@ __global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
 template <int KS, int NV>
 int launch_mma(dim3 grid, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, const int *positions, const int *tiles, const int *block_table,
                int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, const float *slopes, const float *sinks,
-               const float *gate, int ldg, __nv_bfloat16 *out, int ldo, int H, int Hkv, int D, int Dv, float scale, int window, int *status) {
+               const float *gate, int ldg, void *out, int out_f32, int ldo, int H, int Hkv, int Hv, int D, int Dv, int ldv, float scale, int window,
+               int keep_first, int *status) {
     const size_t smem = ((size_t)2 * PAGE * (KS * 16 + 8) + (size_t)2 * PAGE * (NV * 8 + 8)) * 2;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(sink_attention_mma_kernel<KS, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LGML_FAIL("sink_attention_mma: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
     lgml_launch(sink_attention_mma_kernel<KS, NV>, grid, 128, smem, stream, q, ldq, positions, tiles, block_table, max_blocks, k_pages, v_pages,
-                n_pages, slopes, sinks, gate, ldg, out, ldo, H, Hkv, D, Dv, scale, window, status);
+                n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, H, Hkv, Hv, D, Dv, ldv, scale, window, keep_first, status);
     return lgml_launch_status("sink_attention_mma");
 }
 
@@ -454,9 +468,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_kernel(
     const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, const float *__restrict__ slopes, const float *__restrict__ sinks,
-    const float *__restrict__ gate, int ldg, __nv_bfloat16 *__restrict__ out, int ldo, float *__restrict__ part_o,
-    float2 *__restrict__ part_ml, int n_splits, int n_chunks, int H, int Hkv, int D, int Dv, float scale, int window,
-    int v_stage, int *__restrict__ status) {
+    const float *__restrict__ gate, int ldg, void *__restrict__ out, int out_f32, int ldo, float *__restrict__ part_o,
+    float2 *__restrict__ part_ml, int n_splits, int n_chunks, int H, int Hkv, int Hv, int D, int Dv, int ldv, float scale, int window,
+    int keep_first, int v_stage, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float dsm[];
@@ -489,9 +503,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_kernel(
 #pragma unroll
     for (int hh = 0; hh < GH; ++hh) slope2[hh] = (slopes && hh < g_count) ? slopes[h0 + hh] * LOG2E : 0.f;
 
+    // blocks of 32 keys: those of the kept first tokens that lie before the window's, then the window's
     const int b_lo = lo / 32, b_hi = pos / 32;
-    const int per = (b_hi - b_lo + 1 + n_splits - 1) / n_splits;
-    const int b0 = b_lo + split * per, b1 = min(b0 + per, b_hi + 1);
+    const int n_kb = window > 0 ? min((keep_first + 31) / 32, b_lo) : 0;
+    const int n_blocks = n_kb + b_hi - b_lo + 1;
+    const int per = (n_blocks + n_splits - 1) / n_splits;
+    const int b0 = split * per, b1 = min(b0 + per, n_blocks);
+    const int gv = g / (Hkv / Hv);
 
     float m_run[GH], l_run[GH], acc[GH][DEC_COLS];
 #pragma unroll
@@ -502,7 +520,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_kernel(
         for (int c = 0; c < DEC_COLS; ++c) acc[hh][c] = 0.f;
     }
     float *pw = ps + warp * GH * 32;
-    for (int b = b0 + warp; b < b1; b += DEC_WARPS) {
+    for (int bi = b0 + warp; bi < b1; bi += DEC_WARPS) {
+        const int b = bi < n_kb ? bi : b_lo + (bi - n_kb);
         const int pg = b >> 1;
         const int page = pg < max_blocks ? table[pg] : -1;
         if (page < 0 || page >= n_pages) {
@@ -510,17 +529,20 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_kernel(
             continue;
         }
         const size_t cell0 = ((size_t)page * Hkv + g) * PAGE + (size_t)(b & 1) * 32;     // the block's first cell
+        const size_t vcell0 = ((size_t)page * Hv + gv) * PAGE + (size_t)(b & 1) * 32;
         const int j = b * 32 + lane;
-        const bool ok = j >= lo && j <= pos;
-        const int k_first = max(lo - b * 32, 0), k_last = min(pos - b * 32, 31);
-        const __nv_bfloat16 *vbase = v_pages + cell0 * Dv;
+        const bool ok = (j >= lo || j < keep_first) && j <= pos;
+        // the values read: from the first visible key to the last (a key between kept tokens and window weighs 0)
+        const int k_first = b * 32 < keep_first ? 0 : max(lo - b * 32, 0);
+        const int k_last = b * 32 + 31 < lo ? min(keep_first - b * 32, 32) - 1 : min(pos - b * 32, 31);
+        const __nv_bfloat16 *vbase = v_pages + vcell0 * ldv;
         if (v_stage) {
             // the block's visible values on their way into shared memory (through L2) while the scores are computed
             const int chunks = Dv / 8;
             for (int c = lane; c < (k_last - k_first + 1) * chunks; c += 32) {
                 const int kk = k_first + c / chunks, d = (c % chunks) * 8;
                 const uint32_t dst = (uint32_t)__cvta_generic_to_shared(vstage + (size_t)kk * Dv + d);
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vbase + (size_t)kk * Dv + d) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vbase + (size_t)kk * ldv + d) : "memory");
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         }
@@ -610,7 +632,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_kernel(
 #pragma unroll
                     for (int i = 0; i < 2; ++i) {
                         const int d = (lane + 32 * i) * 4;
-                        raw[u][i] = (kb + u <= k_last && d < Dv) ? act_load(reinterpret_cast<const float2 *>(vbase + (size_t)(kb + u) * Dv + d))
+                        raw[u][i] = (kb + u <= k_last && d < Dv) ? act_load(reinterpret_cast<const float2 *>(vbase + (size_t)(kb + u) * ldv + d))
                                                                  : make_float2(0.f, 0.f);
                     }
 #pragma unroll
@@ -634,7 +656,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_kernel(
         } else {
             for (int kk = k_first; kk <= k_last; ++kk) {
                 float vf[DEC_COLS];
-                const __nv_bfloat16 *vrow = vbase + (size_t)kk * Dv;
+                const __nv_bfloat16 *vrow = vbase + (size_t)kk * ldv;
 #pragma unroll
                 for (int c = 0; c < DEC_COLS; ++c) {
                     const int d = lane + 32 * c;
@@ -683,7 +705,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_kernel(
             const float den = l * f + (sinks ? exp2f(sink2 - m_all) : 0.f);
             float r = den > 0.f ? o * f / den : 0.f;
             if (gate) r *= 1.0f / (1.0f + __expf(-act_load(gate + (size_t)t * ldg + (size_t)h * Dv + d)));
-            out[(size_t)t * ldo + (size_t)h * Dv + d] = __float2bfloat16_rn(r);
+            store_out(out, out_f32, (size_t)t * ldo + (size_t)h * Dv + d, r);
         } else {
             part_o[(((size_t)t * H + h) * n_splits + split) * Dv + d] = o;
             if (d == 0) part_ml[((size_t)t * H + h) * n_splits + split] = make_float2(m, l);
@@ -693,7 +715,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_kernel(
 
 __global__ void __launch_bounds__(128) sink_decode_combine_kernel(const float *__restrict__ part_o, const float2 *__restrict__ part_ml,
                                                                   const float *__restrict__ sinks, const float *__restrict__ gate, int ldg,
-                                                                  __nv_bfloat16 *__restrict__ out, int ldo, int n_splits, int H, int Dv) {
+                                                                  void *__restrict__ out, int out_f32, int ldo, int n_splits, int H, int Dv) {
     pdl_trigger();
     pdl_wait();
     __shared__ float f_s[DEC_MAX_SPLITS];
@@ -721,7 +743,7 @@ __global__ void __launch_bounds__(128) sink_decode_combine_kernel(const float *_
         for (int i = 0; i < n_splits; ++i) o += act_load(po + (size_t)i * Dv + d) * f_s[i];
         o *= inv_s;
         if (gate) o *= 1.0f / (1.0f + __expf(-act_load(gate + (size_t)t * ldg + (size_t)h * Dv + d)));
-        out[(size_t)t * ldo + (size_t)h * Dv + d] = __float2bfloat16_rn(o);
+        store_out(out, out_f32, (size_t)t * ldo + (size_t)h * Dv + d, o);
     }
 }
 
@@ -746,9 +768,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_mma_kernel(
     const __nv_bfloat16 *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, const float *__restrict__ slopes, const float *__restrict__ sinks,
-    const float *__restrict__ gate, int ldg, __nv_bfloat16 *__restrict__ out, int ldo, float *__restrict__ part_o,
-    float2 *__restrict__ part_ml, int n_splits, int H, int Hkv, int heads_per_cta, int n_chunks, float scale, int window,
-    int *__restrict__ status) {
+    const float *__restrict__ gate, int ldg, void *__restrict__ out, int out_f32, int ldo, float *__restrict__ part_o,
+    float2 *__restrict__ part_ml, int n_splits, int H, int Hkv, int Hv, int ldv, int heads_per_cta, int n_chunks, float scale, int window,
+    int keep_first, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
     constexpr int D = KS * 16, DV = VS * 16;
@@ -774,10 +796,15 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_mma_kernel(
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int n_pages_seq = pos / PAGE + 1;
     const int first_page = lo / PAGE;
-    const int pps = (n_pages_seq - first_page + n_splits - 1) / n_splits;
-    const int pb = first_page + split * pps;
-    const int pe = min(pb + pps, n_pages_seq);
+    // the pages walked: those of the kept first tokens that lie before the window's, then the window's
+    const int n_kp = window > 0 ? min((keep_first + PAGE - 1) / PAGE, first_page) : 0;
+    const int n_walk = n_kp + n_pages_seq - first_page;
+    const int pps = (n_walk + n_splits - 1) / n_splits;
+    const int pb = split * pps;
+    const int pe = min(pb + pps, n_walk);
     const int n_iter = max(pe - pb, 0);
+    const int kvv = kvh / (Hkv / Hv);
+    auto page_at = [&](int i) { return i < n_kp ? i : first_page + (i - n_kp); };
     const float LOG2E = 1.4426950408889634f;
     const float scale2 = scale * LOG2E;
     // this thread's two heads: columns (lane % 4) * 2 and + 1 of the S^T and O^T fragments
@@ -789,12 +816,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_mma_kernel(
     }
 
     auto load_rows = [&](int it) {
-        const int pg = pb + it;
+        const int pg = page_at(pb + it);
         const int page = pg < max_blocks ? table[pg] : -1;
         const bool have = page >= 0 && page < n_pages;
         if (!have && lane == 0) atomicExch(status, 3);
         const int valid_rows = have ? min(pos - pg * PAGE + 1, PAGE) : 0;
         const size_t cell = ((size_t)(have ? page : 0) * Hkv + kvh) * PAGE + (size_t)warp * WK;
+        const size_t vcell = ((size_t)(have ? page : 0) * Hv + kvv) * PAGE + (size_t)warp * WK;
         __nv_bfloat16 *ks_ = kv_w + (size_t)(it % STAGES) * WARP_STAGE, *vs_ = ks_ + WK * LDK;
 #pragma unroll
         for (int c = lane; c < WK * (D / 8); c += 32) {
@@ -804,7 +832,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_mma_kernel(
 #pragma unroll
         for (int c = lane; c < WK * (DV / 8); c += 32) {
             const int row = c / (DV / 8), col = (c - row * (DV / 8)) * 8;
-            cp_async_16z(vs_ + row * LDV + col, v_pages + (cell + row) * DV + col, warp * WK + row < valid_rows);
+            cp_async_16z(vs_ + row * LDV + col, v_pages + (vcell + row) * ldv + col, warp * WK + row < valid_rows);
         }
     };
 #pragma unroll
@@ -833,7 +861,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_mma_kernel(
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");
         __syncwarp();
-        const int pg = pb + it;
+        const int pg = page_at(pb + it);
         const __nv_bfloat16 *ks_ = kv_w + (size_t)(it % STAGES) * WARP_STAGE, *vs_ = ks_ + WK * LDK;
         const int key_base = pg * PAGE + warp * WK;
         float c[4] = {0.f, 0.f, 0.f, 0.f};
@@ -848,7 +876,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_mma_kernel(
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int kpos = key_base + (lane >> 2) + (i >> 1) * 8;
-            c[i] = (kpos >= lo && kpos <= pos) ? c[i] * scale2 - slope2[i & 1] * (float)(pos - kpos) : -INFINITY;
+            c[i] = ((kpos >= lo || kpos < keep_first) && kpos <= pos) ? c[i] * scale2 - slope2[i & 1] * (float)(pos - kpos) : -INFINITY;
             mx[i & 1] = fmaxf(mx[i & 1], c[i]);
         }
         float corr[2];
@@ -927,7 +955,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_mma_kernel(
             const float den = l * f + (sinks ? exp2f(sink2 - m_all) : 0.f);
             float r = den > 0.f ? o * f / den : 0.f;
             if (gate) r *= 1.0f / (1.0f + __expf(-act_load(gate + (size_t)t * ldg + (size_t)h * DV + d)));
-            out[(size_t)t * ldo + (size_t)h * DV + d] = __float2bfloat16_rn(r);
+            store_out(out, out_f32, (size_t)t * ldo + (size_t)h * DV + d, r);
         } else {
             part_o[(((size_t)t * H + h) * n_splits + split) * DV + d] = o;
             if (d == 0) part_ml[((size_t)t * H + h) * n_splits + split] = make_float2(m, l);
@@ -938,8 +966,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_mma_kernel(
 template <int KS, int VS>
 int launch_decode_mma(dim3 grid, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token,
                       const int *block_table, int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages,
-                      const float *slopes, const float *sinks, const float *gate, int ldg, __nv_bfloat16 *out, int ldo, float *part_o,
-                      float2 *part_ml, int n_splits, int H, int Hkv, int heads_per_cta, int n_chunks, float scale, int window, int *status) {
+                      const float *slopes, const float *sinks, const float *gate, int ldg, void *out, int out_f32, int ldo, float *part_o,
+                      float2 *part_ml, int n_splits, int H, int Hkv, int Hv, int ldv, int heads_per_cta, int n_chunks, float scale, int window,
+                      int keep_first, int *status) {
     constexpr int STAGES = 3;
     constexpr int D = KS * 16, DV = VS * 16;
     const size_t stages = (size_t)DEC_WARPS * ((size_t)STAGES * (PAGE / DEC_WARPS) * (D + 8 + DV + 8) + NH * (PAGE / DEC_WARPS + 8)) * 2;
@@ -950,23 +979,24 @@ int launch_decode_mma(dim3 grid, cudaStream_t stream, const __nv_bfloat16 *q, in
         if (e != cudaSuccess) LGML_FAIL("sink_decode_mma: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
     lgml_launch(sink_decode_mma_kernel<KS, VS, STAGES>, grid, DEC_WARPS * 32, smem, stream, q, ldq, positions, seq_of_token, block_table, max_blocks,
-                k_pages, v_pages, n_pages, slopes, sinks, gate, ldg, out, ldo, part_o, part_ml, n_splits, H, Hkv, heads_per_cta, n_chunks, scale,
-                window, status);
+                k_pages, v_pages, n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, part_o, part_ml, n_splits, H, Hkv, Hv, ldv, heads_per_cta,
+                n_chunks, scale, window, keep_first, status);
     return lgml_launch_status("sink_decode_mma");
 }
 
 template <int GH, bool VEC>
 int launch_decode(dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token,
                   const int *block_table, int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages,
-                  const float *slopes, const float *sinks, const float *gate, int ldg, __nv_bfloat16 *out, int ldo, float *part_o,
-                  float2 *part_ml, int n_splits, int n_chunks, int H, int Hkv, int D, int Dv, float scale, int window, int v_stage,
-                  int *status) {
+                  const float *slopes, const float *sinks, const float *gate, int ldg, void *out, int out_f32, int ldo, float *part_o,
+                  float2 *part_ml, int n_splits, int n_chunks, int H, int Hkv, int Hv, int D, int Dv, int ldv, float scale, int window,
+                  int keep_first, int v_stage, int *status) {
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(sink_decode_kernel<GH, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LGML_FAIL("sink_decode: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
     lgml_launch(sink_decode_kernel<GH, VEC>, grid, DEC_WARPS * 32, smem, stream, q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages,
-                v_pages, n_pages, slopes, sinks, gate, ldg, out, ldo, part_o, part_ml, n_splits, n_chunks, H, Hkv, D, Dv, scale, window, v_stage, status);
+                v_pages, n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, part_o, part_ml, n_splits, n_chunks, H, Hkv, Hv, D, Dv, ldv, scale, window,
+                keep_first, v_stage, status);
     return lgml_launch_status("sink_decode");
 }
 }  // namespace
@@ -1039,11 +1069,14 @@ LGML_API int lgml_sink_attention(const void *q, int dtype, int ldq, const int *p
 
 // The tensor-core form for prompts and portions (bfloat16, pages of 64, head sizes up to 128).
 // tiles: int32 [n_tiles, 4] rows (request row, first token row, tokens <= 64, 0), each within one request.
+// Hv, ldv, keep_first, out_f32: as for lgml_sink_attention (out_f32 != 0: a float32 output).
 LGML_API int lgml_sink_attention_mma(const void *q, int ldq, const int *positions, const int *tiles, int n_tiles, const int *block_table,
                                      int max_blocks, const void *k_pages, const void *v_pages, int n_pages, int page_size,
-                                     const float *slopes, const float *sinks, const float *gate, int ldg, void *out, int ldo, int H, int Hkv,
-                                     int D, int Dv, float scale, int window, int *status, cudaStream_t stream) {
-    LGML_REQUIRE(n_tiles >= 0 && H > 0 && Hkv > 0 && D > 0 && Dv > 0 && max_blocks > 0, "sink_attention_mma: bad sizes");
+                                     const float *slopes, const float *sinks, const float *gate, int ldg, void *out, int out_f32, int ldo, int H,
+                                     int Hkv, int Hv, int D, int Dv, int ldv, float scale, int window, int keep_first, int *status,
+                                     cudaStream_t stream) {
+    LGML_REQUIRE(n_tiles >= 0 && H > 0 && Hkv > 0 && Hv > 0 && D > 0 && Dv > 0 && max_blocks > 0, "sink_attention_mma: bad sizes");
+    LGML_REQUIRE(Hkv % Hv == 0 && ldv >= Dv && keep_first >= 0, "sink_attention_mma: %d key heads on %d value heads, value rows %d apart", Hkv, Hv, ldv);
     LGML_REQUIRE(page_size == PAGE, "sink_attention_mma: pages of %d tokens, this kernel takes %d", page_size, PAGE);
     LGML_REQUIRE(H % Hkv == 0 && H <= 65535, "sink_attention_mma: %d heads on %d KV heads", H, Hkv);
     LGML_REQUIRE(D <= 128 && Dv <= 128, "sink_attention_mma: head sizes %d and %d must be at most 128", D, Dv);
@@ -1054,7 +1087,8 @@ LGML_API int lgml_sink_attention_mma(const void *q, int ldq, const int *position
     const int ks = D <= 32 ? 2 : D <= 64 ? 4 : D <= 96 ? 6 : 8;
     const int nv = Dv <= 32 ? 4 : Dv <= 64 ? 8 : Dv <= 96 ? 12 : 16;
 #define LGML_MMA_ARGS grid, stream, (const __nv_bfloat16 *)q, ldq, positions, tiles, block_table, max_blocks, (const __nv_bfloat16 *)k_pages, \
-                      (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, (__nv_bfloat16 *)out, ldo, H, Hkv, D, Dv, scale, window, status
+                      (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, H, Hkv, Hv, D, Dv, ldv, scale, window, \
+                      keep_first, status
 #define LGML_MMA_NV(KK) \
     switch (nv) { case 4: return launch_mma<KK, 4>(LGML_MMA_ARGS); case 8: return launch_mma<KK, 8>(LGML_MMA_ARGS); \
                   case 12: return launch_mma<KK, 12>(LGML_MMA_ARGS); default: return launch_mma<KK, 16>(LGML_MMA_ARGS); }
@@ -1070,11 +1104,13 @@ LGML_API int lgml_sink_attention_mma(const void *q, int ldq, const int *position
 
 // The split form for decoding and short portions (bfloat16, pages of 64, head sizes up to 256).
 // scratch (float32, n_tokens H n_splits (Dv + 2) elements) is needed when n_splits > 1.
+// Hv, ldv, keep_first, out_f32: as for lgml_sink_attention (out_f32 != 0: a float32 output).
 LGML_API int lgml_sink_decode(const void *q, int ldq, const int *positions, const int *seq_of_token, const int *block_table, int max_blocks,
                               const void *k_pages, const void *v_pages, int n_pages, int page_size, const float *slopes, const float *sinks,
-                              const float *gate, int ldg, void *out, int ldo, float *scratch, int n_splits, int n_tokens, int H, int Hkv,
-                              int D, int Dv, float scale, int window, int *status, cudaStream_t stream) {
-    LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && D > 0 && Dv > 0 && max_blocks > 0, "sink_decode: bad sizes");
+                              const float *gate, int ldg, void *out, int out_f32, int ldo, float *scratch, int n_splits, int n_tokens, int H,
+                              int Hkv, int Hv, int D, int Dv, int ldv, float scale, int window, int keep_first, int *status, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && Hv > 0 && D > 0 && Dv > 0 && max_blocks > 0, "sink_decode: bad sizes");
+    LGML_REQUIRE(Hkv % Hv == 0 && ldv >= Dv && keep_first >= 0, "sink_decode: %d key heads on %d value heads, value rows %d apart", Hkv, Hv, ldv);
     LGML_REQUIRE(page_size == PAGE, "sink_decode: pages of %d tokens, this kernel takes %d", page_size, PAGE);
     LGML_REQUIRE(H % Hkv == 0, "sink_decode: %d heads are no multiple of %d KV heads", H, Hkv);
     LGML_REQUIRE(D <= MAX_D && Dv <= MAX_D, "sink_decode: head sizes %d and %d must be at most %d", D, Dv, MAX_D);
@@ -1086,7 +1122,7 @@ LGML_API int lgml_sink_decode(const void *q, int ldq, const int *positions, cons
     const int group = H / Hkv;
     float *part_o = scratch;
     float2 *part_ml = reinterpret_cast<float2 *>(scratch + (size_t)n_tokens * H * n_splits * Dv);
-    if (D % 32 == 0 && Dv % 32 == 0 && D <= 128 && Dv <= 128 && ldq % 2 == 0 && (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0 &&
+    if (D % 32 == 0 && Dv % 32 == 0 && D <= 128 && Dv <= 128 && ldq % 2 == 0 && ldv % 8 == 0 && (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0 &&
         ((uintptr_t)q & 3) == 0) {
         // head sizes the tensor-core form is built for
         const int n_chunks = (group + NH - 1) / NH;
@@ -1095,8 +1131,8 @@ LGML_API int lgml_sink_decode(const void *q, int ldq, const int *positions, cons
         dim3 grid(n_tokens, Hkv * n_chunks, n_splits);
         int rc = 0;
 #define LGML_DM_ARGS grid, stream, (const __nv_bfloat16 *)q, ldq, positions, seq_of_token, block_table, max_blocks, (const __nv_bfloat16 *)k_pages, \
-                     (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, (__nv_bfloat16 *)out, ldo, part_o, part_ml, n_splits, H, Hkv, \
-                     heads_per_cta, n_chunks, scale, window, status
+                     (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, part_o, part_ml, n_splits, H, Hkv, Hv, ldv, \
+                     heads_per_cta, n_chunks, scale, window, keep_first, status
 #define LGML_DM_VS(KK) \
     switch (Dv / 16) { case 2: rc = launch_decode_mma<KK, 2>(LGML_DM_ARGS); break; case 4: rc = launch_decode_mma<KK, 4>(LGML_DM_ARGS); break; \
                        case 6: rc = launch_decode_mma<KK, 6>(LGML_DM_ARGS); break; default: rc = launch_decode_mma<KK, 8>(LGML_DM_ARGS); break; } \
@@ -1111,13 +1147,13 @@ LGML_API int lgml_sink_decode(const void *q, int ldq, const int *positions, cons
 #undef LGML_DM_ARGS
         if (rc || n_splits == 1) return rc;
         lgml_launch(sink_decode_combine_kernel, dim3(n_tokens, H), 128, 0, stream, (const float *)part_o, (const float2 *)part_ml, sinks, gate, ldg,
-                    (__nv_bfloat16 *)out, ldo, n_splits, H, Dv);
+                    out, out_f32, ldo, n_splits, H, Dv);
         return lgml_launch_status("sink_decode_combine");
     }
     const int gh = group >= 8 ? 8 : group >= 4 ? 4 : group >= 2 ? 2 : 1;       // heads a CTA scores together
     const int n_chunks = (group + gh - 1) / gh;
     LGML_REQUIRE((long long)Hkv * n_chunks <= 65535, "sink_decode: too many heads");
-    const bool vec = D % 8 == 0 && Dv % 4 == 0 && (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
+    const bool vec = D % 8 == 0 && Dv % 4 == 0 && ldv % 8 == 0 && (((uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0;
     // the values of a block go through shared memory when their rows are whole 16-byte pieces (and the floats before them keep that alignment)
     const int v_stage = vec && Dv % 8 == 0 && D % 4 == 0 && (size_t)DEC_WARPS * 32 * Dv * 2 <= 160 * 1024;
     const size_t smem = sizeof(float) * ((size_t)gh * D + (size_t)DEC_WARPS * gh * 32 + 2 * DEC_WARPS * gh + (size_t)DEC_WARPS * gh * Dv) +
@@ -1125,8 +1161,8 @@ LGML_API int lgml_sink_decode(const void *q, int ldq, const int *positions, cons
     dim3 grid(n_tokens, Hkv * n_chunks, n_splits);
     int rc;
 #define LGML_DEC_ARGS grid, smem, stream, (const __nv_bfloat16 *)q, ldq, positions, seq_of_token, block_table, max_blocks, (const __nv_bfloat16 *)k_pages, \
-                      (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, (__nv_bfloat16 *)out, ldo, part_o, part_ml, n_splits, n_chunks, H, \
-                      Hkv, D, Dv, scale, window, v_stage, status
+                      (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, part_o, part_ml, n_splits, n_chunks, H, \
+                      Hkv, Hv, D, Dv, ldv, scale, window, keep_first, v_stage, status
 #define LGML_DEC_GH(G) rc = vec ? launch_decode<G, true>(LGML_DEC_ARGS) : launch_decode<G, false>(LGML_DEC_ARGS); break;
     switch (gh) {
         case 8: LGML_DEC_GH(8)
@@ -1138,6 +1174,6 @@ LGML_API int lgml_sink_decode(const void *q, int ldq, const int *positions, cons
 #undef LGML_DEC_ARGS
     if (rc || n_splits == 1) return rc;
     lgml_launch(sink_decode_combine_kernel, dim3(n_tokens, H), 128, 0, stream, (const float *)part_o, (const float2 *)part_ml, sinks, gate, ldg,
-                (__nv_bfloat16 *)out, ldo, n_splits, H, Dv);
+                out, out_f32, ldo, n_splits, H, Dv);
     return lgml_launch_status("sink_decode_combine");
 }

@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(GU_WARPS * 32) moe_gate_up_kernel(const T *__r
     const int row = blockIdx.x, t = row / top;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int k = threadIdx.x; k < E; k += blockDim.x) hs[k] = to_f32(act_load(h + (size_t)t * ldh + k));
-    int e = ids[row];
+    int e = act_load(ids + row);
     e = e < 0 ? 0 : (e >= X ? X - 1 : e);
     __syncthreads();
     const int f0 = (blockIdx.y * GU_WARPS + warp) * GU_PER_WARP;
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(DN_WARPS * 32) moe_down_kernel(const T *__rest
     for (int j = j0; j < j0 + DN_PER_WARP && j < E; ++j) {
         float total = 0.f;
         for (int s = 0; s < top; ++s) {
-            int e = ids[(size_t)t * top + s];
+            int e = act_load(ids + (size_t)t * top + s);
             e = e < 0 ? 0 : (e >= X ? X - 1 : e);
             const T *d_row = wd + ((size_t)e * E + j) * F;
             float dot = 0.f;
@@ -174,4 +174,224 @@ LGML_API int lgml_moe_experts_rows(const void *h, int dtype, int ldh, const int 
         LGML_FAIL("moe_experts_rows: unknown type %d", dtype);
     }
     return lgml_launch_status("moe_experts_rows");
+}
+
+// ---------------------------------------------------------------------------------------------
+// The grouped form, bfloat16, for many tokens: the (token, chosen expert) rows are sorted by expert,
+// cut into tiles of 64 rows of one expert, and every tile is a product on tensor cores (mma.sync
+// m16n8k16, float32 accumulation) against that expert's matrices, which are then read once per tile
+// and not once per row.
+//   moe_group        counts the rows per expert, lists them expert by expert and writes the tiles
+//                    (expert, first row of the list, rows); one block, no host in the loop, so the
+//                    step stays a fixed sequence of launches whatever the router chose
+//   moe_tile_product C[64 rows, 64 columns] of a tile: MODE 0 gathers the tokens' rows of h, takes 32
+//                    gate and 32 up features at once and writes silu(gate) * up; MODE 1 reads the
+//                    activations and writes the down product times the row's weight, float32
+//   moe_sum          out[t] = the rows of token t added in the order of its chosen experts
+// A row's result does not depend on where in a tile it lies, so the order in which rows were
+// listed (atomics) does not show in the output.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr int G_TM = 64, G_TN = 64, G_TK = 32, G_LD = G_TK + 8;
+
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int *__restrict__ ids, int n_rows, int X, int *__restrict__ rows,
+                                                         int *__restrict__ tiles, int *__restrict__ n_tiles, int max_tiles) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ int sh[];         // counts[X], first[X], cursor[X], tile0[X]
+    int *counts = sh, *first = sh + X, *cursor = sh + 2 * X, *tile0 = sh + 3 * X;
+    for (int e = threadIdx.x; e < X; e += blockDim.x) counts[e] = 0, cursor[e] = 0;
+    __syncthreads();
+    for (int r = threadIdx.x; r < n_rows; r += blockDim.x) {
+        int e = act_load(ids + r);
+        e = e < 0 ? 0 : (e >= X ? X - 1 : e);
+        atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tl = 0;
+        for (int e = 0; e < X; ++e) {
+            first[e] = at, tile0[e] = tl;
+            at += counts[e];
+            tl += (counts[e] + G_TM - 1) / G_TM;
+        }
+        *n_tiles = tl < max_tiles ? tl : max_tiles;
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < n_rows; r += blockDim.x) {
+        int e = act_load(ids + r);
+        e = e < 0 ? 0 : (e >= X ? X - 1 : e);
+        rows[first[e] + atomicAdd(&cursor[e], 1)] = r;
+    }
+    for (int e = threadIdx.x; e < X; e += blockDim.x) {
+        const int nt = (counts[e] + G_TM - 1) / G_TM;
+        for (int i = 0; i < nt; ++i) {
+            const int tl = tile0[e] + i;
+            if (tl >= max_tiles) break;
+            tiles[tl * 3] = e;
+            tiles[tl * 3 + 1] = first[e] + i * G_TM;
+            tiles[tl * 3 + 2] = min(G_TM, counts[e] - i * G_TM);
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t g_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void g_ldmatrix_x4(uint32_t (&r)[4], const void *p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(g_smem_u32(p)));
+}
+__device__ __forceinline__ void g_mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void g_cp16(void *dst, const void *src, bool valid) {
+    const int bytes = valid ? 16 : 0;   // 0: zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(g_smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+
+// MODE 0: a = h (rows gathered by token), b = 32 rows of w0[e] (gate) then 32 of w1[e] (up) from feature 32 blockIdx.y on,
+//         out0 = act [n_rows, N] bfloat16.  K = E, N = F.
+// MODE 1: a = act rows, b = 64 rows of w0[e] (down) from column 64 blockIdx.y on, out1 = y [n_rows, N] float32, times wts[row].
+//         K = F, N = E.
+template <int MODE>
+__global__ void __launch_bounds__(128) moe_tile_product_kernel(const __nv_bfloat16 *__restrict__ a, int lda, const int *__restrict__ rows,
+                                                               const int *__restrict__ tiles, const int *__restrict__ n_tiles,
+                                                               const __nv_bfloat16 *__restrict__ w0, const __nv_bfloat16 *__restrict__ w1,
+                                                               const float *__restrict__ wts, __nv_bfloat16 *__restrict__ out0,
+                                                               float *__restrict__ out1, int K, int N, int top) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ __align__(16) __nv_bfloat16 As[2][G_TM * G_LD];
+    __shared__ __align__(16) __nv_bfloat16 Bs[2][G_TN * G_LD];
+    __shared__ int row_of[G_TM];
+    const int tile = blockIdx.x;
+    if (tile >= act_load(n_tiles)) return;
+    const int e = act_load(tiles + tile * 3), r0 = act_load(tiles + tile * 3 + 1), n_r = act_load(tiles + tile * 3 + 2);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int mat = lane >> 3, mrow = lane & 7;
+    if (threadIdx.x < G_TM) row_of[threadIdx.x] = threadIdx.x < n_r ? act_load(rows + r0 + threadIdx.x) : -1;
+    __syncthreads();
+    constexpr int HALF = G_TN / 2;
+    const int c0 = MODE == 0 ? blockIdx.y * HALF : blockIdx.y * G_TN;     // first feature (MODE 0) or column (MODE 1)
+
+    auto issue = [&](int kt, int buf) {
+        const int k0 = kt * G_TK;
+        for (int c = threadIdx.x; c < G_TM * (G_TK / 8); c += 128) {
+            const int r = c / (G_TK / 8), col = (c - r * (G_TK / 8)) * 8;
+            const int row = row_of[r];
+            const bool ok = row >= 0 && k0 + col < K;
+            const size_t src_row = MODE == 0 ? (size_t)(row >= 0 ? row / top : 0) : (size_t)(row >= 0 ? row : 0);
+            g_cp16(&As[buf][r * G_LD + col], a + src_row * lda + (ok ? k0 + col : 0), ok);
+        }
+        for (int c = threadIdx.x; c < G_TN * (G_TK / 8); c += 128) {
+            const int r = c / (G_TK / 8), col = (c - r * (G_TK / 8)) * 8;
+            const __nv_bfloat16 *base;
+            int n;
+            if (MODE == 0) {
+                n = c0 + (r % HALF);
+                base = (r < HALF ? w0 : w1) + ((size_t)e * N + (n < N ? n : 0)) * K;
+            } else {
+                n = c0 + r;
+                base = w0 + ((size_t)e * N + (n < N ? n : 0)) * K;
+            }
+            const bool ok = n < N && k0 + col < K;
+            g_cp16(&Bs[buf][r * G_LD + col], base + (ok ? k0 + col : 0), ok);
+        }
+    };
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    const int n_kt = (K + G_TK - 1) / G_TK;
+    issue(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int kt = 0; kt < n_kt; ++kt) {
+        const int buf = kt & 1;
+        if (kt + 1 < n_kt) issue(kt + 1, buf ^ 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < G_TK / 16; ++ks) {
+            uint32_t af[4];
+            g_ldmatrix_x4(af, &As[buf][(warp * 16 + (mat & 1) * 8 + mrow) * G_LD + ks * 16 + (mat >> 1) * 8]);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b[4];
+                g_ldmatrix_x4(b, &Bs[buf][(np * 16 + (mat >> 1) * 8 + mrow) * G_LD + ks * 16 + (mat & 1) * 8]);
+                g_mma_bf16(acc[2 * np], af, b[0], b[1]);
+                g_mma_bf16(acc[2 * np + 1], af, b[2], b[3]);
+            }
+        }
+        __syncthreads();            // the buffer is free for the copy after next
+    }
+    // rows lane / 4 and + 8 of the warp's 16; columns 8 nt + (lane % 4) * 2 and + 1
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int r = warp * 16 + (lane >> 2) + rr * 8;
+        const int row = row_of[r];
+        if (row < 0) continue;
+        if (MODE == 0) {
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int f = c0 + nt * 8 + (lane & 3) * 2 + i;
+                    if (f >= N) continue;
+                    const float g = acc[nt][rr * 2 + i], u = acc[nt + 4][rr * 2 + i];
+                    out0[(size_t)row * N + f] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+                }
+        } else {
+            const float w = act_load(wts + row);
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int j = c0 + nt * 8 + (lane & 3) * 2 + i;
+                    if (j < N) out1[(size_t)row * N + j] = acc[nt][rr * 2 + i] * w;
+                }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) moe_sum_kernel(const float *__restrict__ y, float *__restrict__ out, int n_tokens, int E, int top) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t total = (size_t)n_tokens * E;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / E, j = i - t * E;
+        float s = 0.f;
+        for (int k = 0; k < top; ++k) s += act_load(y + (t * top + k) * E + j);
+        out[i] = s;
+    }
+}
+}  // namespace
+
+// h bfloat16 [n, ldh]; ids / wts [n, top]; the experts' matrices stacked, bfloat16; scratch of the caller: rows int32 [n top],
+// tiles int32 [3 max_tiles + 1] (the last word: the number of tiles), act bfloat16 [n top, F], y float32 [n top, E];
+// out float32 [n, E].  E and F multiples of 8, ldh too.
+LGML_API int lgml_moe_experts_grouped(const void *h, int ldh, const int *ids, const float *wts, const void *wg, const void *wu, const void *wd,
+                                      int *rows, int *tiles, int max_tiles, void *act, float *y, float *out, int n_tokens, int E, int F, int X,
+                                      int top, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && E > 0 && F > 0 && X > 0 && top > 0, "moe_experts_grouped: bad sizes");
+    LGML_REQUIRE(E % 8 == 0 && F % 8 == 0 && ldh % 8 == 0, "moe_experts_grouped: widths %d, %d and the row stride %d must be multiples of 8", E, F, ldh);
+    LGML_REQUIRE((((uintptr_t)h | (uintptr_t)wg | (uintptr_t)wu | (uintptr_t)wd | (uintptr_t)act) & 15) == 0, "moe_experts_grouped: operands must be 16-byte aligned");
+    LGML_REQUIRE(X <= 8192, "moe_experts_grouped: at most 8192 experts");
+    if (n_tokens == 0) return 0;
+    const int n_rows = n_tokens * top;
+    const int need = (n_rows + G_TM - 1) / G_TM + (X < n_rows ? X : n_rows);
+    LGML_REQUIRE(max_tiles >= need, "moe_experts_grouped: room for %d tiles, %d may be needed", max_tiles, need);
+    int *n_tiles = tiles + 3 * max_tiles;
+    lgml_launch(moe_group_kernel, 1, 1024, sizeof(int) * 4 * (size_t)X, stream, ids, n_rows, X, rows, tiles, n_tiles, max_tiles);
+    dim3 g0(max_tiles, (F + G_TN / 2 - 1) / (G_TN / 2)), g1(max_tiles, (E + G_TN - 1) / G_TN);
+    LGML_REQUIRE(g0.y <= 65535 && g1.y <= 65535, "moe_experts_grouped: too many columns");
+    lgml_launch(moe_tile_product_kernel<0>, g0, 128, 0, stream, (const __nv_bfloat16 *)h, ldh, (const int *)rows, (const int *)tiles,
+                (const int *)n_tiles, (const __nv_bfloat16 *)wg, (const __nv_bfloat16 *)wu, (const float *)nullptr, (__nv_bfloat16 *)act,
+                (float *)nullptr, E, F, top);
+    lgml_launch(moe_tile_product_kernel<1>, g1, 128, 0, stream, (const __nv_bfloat16 *)act, F, (const int *)rows, (const int *)tiles,
+                (const int *)n_tiles, (const __nv_bfloat16 *)wd, (const __nv_bfloat16 *)nullptr, wts, (__nv_bfloat16 *)nullptr, y, F, E, top);
+    const size_t total = (size_t)n_tokens * E;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    lgml_launch(moe_sum_kernel, blocks, 256, 0, stream, (const float *)y, out, n_tokens, E, top);
+    return lgml_launch_status("moe_experts_grouped");
 }

@@ -27,6 +27,7 @@ _STATUS_TEXT = {
 
 AHEAD_BYTES = 24 << 20      # weights asked of L2 ahead, per layer (measured best at 24 to 32 MiB)
 AHEAD_MAX_BATCH = 4         # ... in captured steps of at most this many requests (at 8 the step gets slower)
+MOE_GROUPED_ROWS = 32       # (token, expert) rows of a step from which the experts run as grouped tiles
 MAX_RESULT = 4096     # most sampled rows of a step whose ids travel with the status word
 
 
@@ -113,14 +114,12 @@ class Runtime:
         ``keep_first`` tokens stay visible) and an output gate, of the step's queries over the
         cache.  Keys and values have head sizes of their own; the values may have fewer heads
         than the keys, or be the first entries of the key cells."""
-        plain = (not keep_first and cache.v.shape[1] == cache.k.shape[1] and cache.v.is_contiguous() and out.dtype == q.dtype)
-        if not plain:
-            # the general form knows every option
-            return ops.sink_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
-                                      window, self.status, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first)
-        if (self.dtype == torch.bfloat16 and self.attention_backend != "ref" and batch.max_q_len > ops.DECODE_MAX_Q
-                and cache.k.shape[2] == 64 and cache.k.shape[3] <= 128 and cache.v.shape[3] <= 128):
-            if ops.sink_twin_supports(q, out, cache.k, cache.v, gate):
+        bf16 = self.dtype == torch.bfloat16 and self.attention_backend != "ref" and cache.k.shape[2] == 64
+        # what only this family's own kernels know: kept first tokens, value heads of their own count, values that are a
+        # column range of the key cells, a float32 result
+        plain = not keep_first and cache.v.shape[1] == cache.k.shape[1] and cache.v.is_contiguous() and out.dtype == q.dtype
+        if bf16 and batch.max_q_len > ops.DECODE_MAX_Q and cache.k.shape[3] <= 128 and cache.v.shape[3] <= 128:
+            if plain and ops.sink_twin_supports(q, out, cache.k, cache.v, gate):
                 # prompts and portions, keys and values of one head size (64 or 128): the two-tile tcgen05 kernel
                 hkv = cache.k.shape[1]
                 tiles = batch.attention_tiles(ops.prefill_twin_tile_tokens(n_heads, hkv))
@@ -129,20 +128,23 @@ class Runtime:
             # every other head size up to 128: tiles of 64 tokens, mma.sync
             tiles = batch.attention_tiles(ops.SINK_TILE_TOKENS)
             return ops.sink_attention_mma(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window,
-                                          self.status, slopes=slopes, sinks=sinks, gate=gate)
-        if self.dtype == torch.bfloat16 and self.attention_backend != "ref" and cache.k.shape[2] == 64:
-            # decoding and short portions: every token's keys in ranges, the heads of a KV head together
+                                          self.status, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first)
+        if bf16 and cache.k.shape[3] <= 256 and cache.v.shape[3] <= 256:
+            # decoding and short portions (and prompts of head sizes beyond 128): every token's keys in ranges, the heads of a KV head together
             hkv = cache.k.shape[1]
-            reach = min(window, batch.max_kv_len) if window else batch.max_kv_len
+            reach = (min(window, batch.max_kv_len) if window else batch.max_kv_len) + (keep_first if window else 0)
             n_splits = ops.sink_decode_splits(q.shape[0], hkv, n_heads // hkv, reach)
             return ops.sink_decode(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale, window,
-                                   self.status, n_splits, slopes=slopes, sinks=sinks, gate=gate)
+                                   self.status, n_splits, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first)
         return ops.sink_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
-                                  window, self.status, slopes=slopes, sinks=sinks, gate=gate)
+                                  window, self.status, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first)
 
     # ---- mixture of experts ------------------------------------------------------------
     def moe_experts(self, h, ids, wts, w_gate, w_up, w_down) -> torch.Tensor:
-        """The chosen experts' weighted outputs, float32 [tokens, width]."""
+        """The chosen experts' weighted outputs, float32 [tokens, width]: a block per (token, expert) for few
+        tokens and on the 32-bit path, tiles of one expert's rows on tensor cores for many."""
+        if ids.numel() >= MOE_GROUPED_ROWS and ops.moe_grouped_supports(h, w_gate):
+            return ops.moe_experts_grouped(h, ids, wts, w_gate, w_up, w_down)
         return ops.moe_experts_rows(h, ids, wts, w_gate, w_up, w_down)
 
     # ---- faults ------------------------------------------------------------------------

@@ -585,24 +585,24 @@ SINK_TILE_TOKENS = 64      # query tokens per tile of the tensor-core sink atten
 def sink_attention_mma(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
                        v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int, status: torch.Tensor,
                        slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
-                       gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       gate: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
     """``sink_attention`` for prompts and portions on tensor cores: bfloat16, pages of 64, head sizes
     up to 128.  ``tiles`` int32 [n_tiles, 4]: (request row, first token row, tokens <= 64, 0), each
-    tile within one request (``StepBatch.attention_tiles(SINK_TILE_TOKENS)``)."""
+    tile within one request (``StepBatch.attention_tiles(SINK_TILE_TOKENS)``).  ``out`` bfloat16 or float32."""
     _need(q, "queries", torch.bfloat16, 2)
-    _need(out, "attention output", torch.bfloat16, 2)
+    _need(out, "attention output", ndim=2)
     ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
     n = q.shape[0]
     _need(k_pages, "key pages", torch.bfloat16, 4)
     _need(v_pages, "value pages", torch.bfloat16, 4)
     n_pages, hkv, page, d = k_pages.shape
-    dv = v_pages.shape[3]
+    hv, dv, ldv = _value_pages(v_pages, k_pages, "sink_attention_mma")
     _need(positions, "positions", torch.int32, 1)
     _need(tiles, "tiles", torch.int32, 2)
     _need(block_table, "block table", torch.int32, 2)
-    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * dv) or tiles.shape[1] != 4:
-        raise KernelError(f"sink_attention_mma: q {tuple(q.shape)} / out {tuple(out.shape)} / tiles {tuple(tiles.shape)} do not fit")
-    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous() or not tiles.is_contiguous():
+    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * dv) or tiles.shape[1] != 4 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"sink_attention_mma: q {tuple(q.shape)} / out {tuple(out.shape)} {out.dtype} / tiles {tuple(tiles.shape)} do not fit")
+    if not k_pages.is_contiguous() or not block_table.is_contiguous() or not tiles.is_contiguous():
         raise KernelError("sink_attention_mma: pages, block table and tiles must be contiguous")
     for t, what in ((slopes, "slopes"), (sinks, "sinks")):
         if t is not None:
@@ -616,11 +616,12 @@ def sink_attention_mma(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Te
         if tuple(gate.shape) != (n, n_heads * dv):
             raise KernelError(f"sink_attention_mma: gate {tuple(gate.shape)} is not [{n}, {n_heads * dv}]")
     fn = _fn("attention_sink", "lgml_sink_attention_mma", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
-                                                           c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                                           c_float, c_int, c_void_p, c_void_p])
+                                                           c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                           c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
     _check("attention_sink", fn(_ptr(q), ldq, _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(block_table), block_table.shape[1], _ptr(k_pages),
-                                _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), ldo, n_heads, hkv, d, dv,
-                                float(scale), int(window or 0), _ptr(status), _stream()), "sink_attention_mma")
+                                _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), 1 if out.dtype == torch.float32 else 0,
+                                ldo, n_heads, hkv, hv, d, dv, ldv, float(scale), int(window or 0), int(keep_first or 0), _ptr(status), _stream()),
+           "sink_attention_mma")
     return out
 
 
@@ -687,23 +688,25 @@ def sink_decode_splits(n_tokens: int, n_kv_heads: int, group: int, reach: int) -
 
 def sink_decode(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
                 v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int, status: torch.Tensor, n_splits: int,
-                slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                keep_first: int = 0) -> torch.Tensor:
     """``sink_attention`` for decoding and short portions (bfloat16, pages of 64): each token's keys cut into
-    ``n_splits`` ranges, the query heads of a KV head scored together, the ranges merged by a second kernel."""
+    ``n_splits`` ranges, the query heads of a KV head scored together, the ranges merged by a second kernel.
+    ``out`` bfloat16 or float32."""
     _need(q, "queries", torch.bfloat16, 2)
-    _need(out, "attention output", torch.bfloat16, 2)
+    _need(out, "attention output", ndim=2)
     ldq, ldo = _rows_contiguous(q, "queries"), _rows_contiguous(out, "attention output")
     n = q.shape[0]
     _need(k_pages, "key pages", torch.bfloat16, 4)
     _need(v_pages, "value pages", torch.bfloat16, 4)
     n_pages, hkv, page, d = k_pages.shape
-    dv = v_pages.shape[3]
+    hv, dv, ldv = _value_pages(v_pages, k_pages, "sink_decode")
     _need(positions, "positions", torch.int32, 1)
     _need(seq_of_token, "request index of tokens", torch.int32, 1)
     _need(block_table, "block table", torch.int32, 2)
-    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * dv):
-        raise KernelError(f"sink_decode: q {tuple(q.shape)} / out {tuple(out.shape)} do not fit {n_heads} heads of {d} and {dv}")
-    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
+    if q.shape[1] != n_heads * d or out.shape != (n, n_heads * dv) or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"sink_decode: q {tuple(q.shape)} / out {tuple(out.shape)} {out.dtype} do not fit {n_heads} heads of {d} and {dv}")
+    if not k_pages.is_contiguous() or not block_table.is_contiguous():
         raise KernelError("sink_decode: pages and block table must be contiguous")
     for t, what in ((slopes, "slopes"), (sinks, "sinks")):
         if t is not None:
@@ -718,11 +721,12 @@ def sink_decode(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Te
             raise KernelError(f"sink_decode: gate {tuple(gate.shape)} is not [{n}, {n_heads * dv}]")
     scratch = torch.empty(n * n_heads * n_splits * (dv + 2), dtype=torch.float32, device=q.device) if n_splits > 1 else None
     fn = _fn("attention_sink", "lgml_sink_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
-                                                    c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                    c_float, c_int, c_void_p, c_void_p])
+                                                    c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                    c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
     _check("attention_sink", fn(_ptr(q), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(k_pages),
-                                _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), ldo, _ptr(scratch),
-                                int(n_splits), n, n_heads, hkv, d, dv, float(scale), int(window or 0), _ptr(status), _stream()), "sink_decode")
+                                _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), 1 if out.dtype == torch.float32 else 0,
+                                ldo, _ptr(scratch), int(n_splits), n, n_heads, hkv, hv, d, dv, ldv, float(scale), int(window or 0), int(keep_first or 0),
+                                _ptr(status), _stream()), "sink_decode")
     return out
 
 
@@ -856,6 +860,49 @@ def moe_experts_rows(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_ga
                                               c_int, c_int, c_int, c_void_p])
     _check("moe", fn(_ptr(h), dtype_code(h.dtype), ldh, _ptr(ids), _ptr(wts), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _ptr(act), _ptr(out), n, E, F, X,
                      top, _stream()), "moe_experts_rows")
+    return out
+
+
+MOE_TILE_ROWS = 64
+
+
+def moe_grouped_supports(h: torch.Tensor, w_gate: torch.Tensor) -> bool:
+    """Whether ``moe_experts_grouped`` takes these operands: bfloat16, widths that are multiples of 8."""
+    return (h.dtype == torch.bfloat16 and h.dim() == 2 and h.stride(1) == 1 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
+            and w_gate.shape[1] % 8 == 0 and w_gate.shape[2] % 8 == 0)
+
+
+def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """``moe_experts_rows`` for many tokens, bfloat16: the (token, chosen expert) rows sorted by expert on
+    the device and cut into tiles of 64 rows of one expert, each tile a product on tensor cores; float32
+    [tokens, E].  No host value is read: the launches are the same whatever the router chose."""
+    _need(h, "experts' input", torch.bfloat16, 2)
+    for t, what in ((w_gate, "gate"), (w_up, "up"), (w_down, "down")):
+        _need(t, f"experts' {what} matrices", torch.bfloat16, 3)
+        if not t.is_contiguous():
+            raise KernelError(f"moe_experts_grouped: the {what} matrices must be contiguous")
+    _need(ids, "chosen experts", torch.int32, 2)
+    _need(wts, "experts' weights", torch.float32, 2)
+    ldh = _rows_contiguous(h, "experts' input")
+    n, E = h.shape
+    X, F, _ = w_gate.shape
+    top = ids.shape[1]
+    if tuple(w_gate.shape) != (X, F, E) or tuple(w_up.shape) != (X, F, E) or tuple(w_down.shape) != (X, E, F) or tuple(ids.shape) != (n, top) \
+            or tuple(wts.shape) != (n, top) or not ids.is_contiguous() or not wts.is_contiguous():
+        raise KernelError(f"moe_experts_grouped: shapes disagree: h {tuple(h.shape)}, gate {tuple(w_gate.shape)}, down {tuple(w_down.shape)}, ids {tuple(ids.shape)}")
+    if not moe_grouped_supports(h, w_gate):
+        raise KernelError("moe_experts_grouped: widths and row strides must be multiples of 8 and the input 16-byte aligned")
+    n_rows = n * top
+    max_tiles = -(-n_rows // MOE_TILE_ROWS) + min(X, n_rows)
+    rows = torch.empty(n_rows, dtype=torch.int32, device=h.device)
+    tiles = torch.empty(3 * max_tiles + 1, dtype=torch.int32, device=h.device)
+    act = torch.empty((n_rows, F), dtype=torch.bfloat16, device=h.device)
+    y = torch.empty((n_rows, E), dtype=torch.float32, device=h.device)
+    out = torch.empty((n, E), dtype=torch.float32, device=h.device)
+    fn = _fn("moe", "lgml_moe_experts_grouped", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check("moe", fn(_ptr(h), ldh, _ptr(ids), _ptr(wts), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _ptr(rows), _ptr(tiles), max_tiles, _ptr(act),
+                     _ptr(y), _ptr(out), n, E, F, X, top, _stream()), "moe_experts_grouped")
     return out
 
 

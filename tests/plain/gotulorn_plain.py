@@ -113,12 +113,16 @@ def dense_ff(h, W, p, f):
     return (g / (1.0 + np.exp(-1.702 * g)) * (u + 1.0)) @ W[p + ".down"].T
 
 
-def routed_ff(h, W, p, f):
+def routed_ff(h, W, p, f, gaps=None):
     """Every token goes through its ``top`` experts with the largest router logits; their weights are
-    the softmax over those logits alone."""
+    the softmax over those logits alone.  ``gaps`` (a list) receives, per token, how far the last
+    chosen logit lies above the first one left out (infinite when every expert is chosen)."""
     n_exp, top = f["router"]["experts"], f["router"]["top"]
     z = h @ W[p + ".router"].T + W[p + ".router.b"]
     out = np.zeros((h.shape[0], W[p + ".e0.down"].shape[0]))
+    if gaps is not None:
+        ranked = -np.sort(-z, axis=1)
+        gaps.append(ranked[:, top - 1] - ranked[:, top] if top < n_exp else np.full(h.shape[0], np.inf))
     for t in range(h.shape[0]):
         chosen = np.argsort(-z[t], kind="stable")[:top]
         w = np.exp(z[t, chosen] - z[t, chosen].max())
@@ -134,8 +138,9 @@ def norm_of(W, name, x):
     return dyt(x, W[name], W[name + ".b"], W[name + ".alpha"])
 
 
-def forward(cfg, W, tokens, return_layers=False):
-    """Logits [T, vocab] of a whole sequence (and, on request, the residual stream after every layer)."""
+def forward(cfg, W, tokens, return_layers=False, router_gaps=None):
+    """Logits [T, vocab] of a whole sequence (and, on request, the residual stream after every layer;
+    ``router_gaps``, a list, receives one array per routed layer: see ``routed_ff``)."""
     eps = cfg["norm"]["eps"]
     x = W["embed"][np.asarray(tokens)] * cfg["embedding"]["scale"]
     x = norm_of(W, "embed.norm", x)
@@ -156,7 +161,7 @@ def forward(cfg, W, tokens, return_layers=False):
         f = layer.get("mlp")
         if f is not None:
             h = norm_of(W, p + ".norm2", x)
-            x = x + (dense_ff(h, W, p + ".mlp", f) if f["kind"] == "dense" else routed_ff(h, W, p + ".mlp", f))
+            x = x + (dense_ff(h, W, p + ".mlp", f) if f["kind"] == "dense" else routed_ff(h, W, p + ".mlp", f, router_gaps))
         layers.append(x.copy())
     logits = norm_of(W, "final.norm", x) @ W["head"].T
     return (logits, layers) if return_layers else logits
