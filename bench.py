@@ -16,7 +16,7 @@ measured copy bandwidth, and ``roofline_points`` the same fraction for every bat
 
 ``--shape llama32_3b`` runs that shape's own workload (32 prompts of 128 to 4,096 tokens in
 portions of 512 beside decodes, 512 new tokens each) through ``Engine.generate``;
-``--shape llama2_13b`` decodes at batch 16 after 3,584-token prompts; ``--design lefulorn``
+``--shape llama2_13b`` decodes at batch 16 after 3,584-token prompts; ``--design lefulorn`` (or ``gotulorn``)
 times that design beside the Llama decoder at equal layer sizes; ``--cpu-baseline`` times the
 plain CPU implementation at the tiny configurations.
 """
@@ -293,6 +293,34 @@ def lefulorn_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int
             "layers": [dict(att if i % 2 == 0 else dl) for i in range(layers)]}
 
 
+def gotulorn_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, layers: int, window: int, vocab: int) -> dict:
+    """Gotulorn with layers of a real model's size: differential attention (two maps of half the head size, values of
+    the head size, a window that keeps the first 4 tokens; every second one of them reads the keys and values of the one
+    before) and latent attention (a latent of 96 and a rotated part of 32, which is what the tensor-core attention
+    kernels take) in turn; the clamped gated feed-forward on the attention layers, 8 experts of a quarter of its inner
+    width, 2 of them chosen, on the latent layers."""
+    inner = (2 * ff // 3 + 255) // 256 * 256
+    out = []
+    last_own = None
+    for i in range(layers):
+        if i % 2 == 0:
+            m = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim // 2, "vdim": head_dim, "scale": (head_dim // 2) ** -0.5, "diff": 0.3,
+                 "mask": {"size": window, "keep_first": 4}}
+            if last_own is not None:
+                m["kv_from"], last_own = last_own, None
+            else:
+                last_own = i
+            out.append({"type": "attention", "mixer": m, "mlp": {"kind": "dense", "ff": inner, "limit": 7.0}})
+        else:
+            m = {"heads": heads, "dim": head_dim // 2, "rot_dim": 32, "vdim": head_dim // 2, "kv_rank": 96, "scale": (head_dim // 2 + 32) ** -0.5,
+                 "rot": {"base": 10000.0, "dims": 32}}
+            out.append({"type": "latent_attention", "mixer": m,
+                        "mlp": {"kind": "moe", "expert": {"ff": inner // 4}, "router": {"experts": 8, "top": 2}}})
+    return {"architecture": "Gotulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "layers": out}
+
+
+DESIGN_SHAPES = {"lefulorn": lefulorn_shape, "gotulorn": gotulorn_shape}
+
 DESIGN_SIZES = {          # name -> width, heads, KV heads, head size, dense inner width, layers
     "w2048": (2048, 16, 4, 128, 8192, 4),
     "w4096": (4096, 32, 8, 128, 14336, 4),
@@ -301,7 +329,7 @@ DESIGN_SIZES = {          # name -> width, heads, KV heads, head size, dense inn
 
 def run_design_compare(args, warmup: int) -> dict:
     """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 after 2,048-token prompts) of the
-    Lefulorn design and of the Llama decoder with layers of the same sizes (the gated feed-forward's inner width
+    design ``args.design`` and of the Llama decoder with layers of the same sizes (the gated feed-forward's inner width
     is two thirds of the dense one's: the same number of weights), random weights, with the device time of every
     kernel class in one prefill step and one decode step of each."""
     import torch
@@ -323,7 +351,7 @@ def run_design_compare(args, warmup: int) -> dict:
         llama = {**LLAMA31_8B, "num_hidden_layers": L, "hidden_size": E, "num_attention_heads": H, "num_key_value_heads": G, "head_dim": D,
                  "intermediate_size": (2 * F // 3 + 255) // 256 * 256, "vocab_size": vocab, "max_position_embeddings": CONTEXT}
         row = {}
-        for design, d in (("lefulorn", lefulorn_shape(E, H, G, D, F, L, window, vocab)), ("llama", llama)):
+        for design, d in ((args.design, DESIGN_SHAPES[args.design](E, H, G, D, F, L, window, vocab)), ("llama", llama)):
             cfg = config_from_dict(d)
             runner = ModelRunner.from_config(cfg, seed=0, dtype=torch.bfloat16, n_pages=BATCH * (CONTEXT // 64) + 8, max_slots=BATCH,
                                              max_step_tokens=2048)
@@ -355,8 +383,8 @@ def run_design_compare(args, warmup: int) -> dict:
             torch.cuda.empty_cache()
         out[name] = row
     clock_rec = clocks.stop()
-    first = next(iter(out.values()))["lefulorn"]
-    return {"metric": f"Lefulorn beside the Llama decoder at equal layer sizes: prefill of {PREFILL_TOKENS:,} tokens and decode at batch {BATCH}",
+    first = next(iter(out.values()))[args.design]
+    return {"metric": f"{args.design.capitalize()} beside the Llama decoder at equal layer sizes: prefill of {PREFILL_TOKENS:,} tokens and decode at batch {BATCH}",
             "value": first["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
             "ms_per_step": first["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic: random weights N(0, 0.02), uniform-random token ids",
@@ -410,7 +438,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0, help="context (tokens a request may hold) instead of the shape's own")
     ap.add_argument("--prefill-tokens", type=int, default=0, help="tokens of the timed prompt instead of 2,048 (read in portions of 2,048)")
     ap.add_argument("--no-kernel-times", action="store_true", help="leave out the per-kernel-class times of a decode step")
-    ap.add_argument("--design", default="", choices=["", "lefulorn"], help="time this design beside the Llama decoder at equal layer sizes "
+    ap.add_argument("--design", default="", choices=["", "lefulorn", "gotulorn"], help="time this design beside the Llama decoder at equal layer sizes "
                     "(prefill and decode, with kernel-class times) instead of the headline workload")
     ap.add_argument("--cpu-baseline", action="store_true", help="time the plain CPU implementation at the tiny configurations and stop")
     args = ap.parse_args()

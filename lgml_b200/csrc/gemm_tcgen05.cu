@@ -130,7 +130,9 @@ struct Params {
     int tiles_a, tiles_b;   // tiles along the rows of A and of B; tile index = tile_b * tiles_a + tile_a
     int kb_per_split; // k blocks per grid.z slice
     int transposed;   // 1: the tile is y^T (A = weights, B = tokens)
-    int swiglu;       // 1: feature rows come in (gate, up) pairs; the output is silu(gate) * up, half as wide; 2: the output is relu(y)^2
+    int swiglu;       // 1: feature rows come in (gate, up) pairs; the output is silu(gate) * up, half as wide; 2: the output is relu(y)^2;
+                      // 3: pairs as for 1, the output is g sigmoid(act_alpha g) (u + 1) with g = min(gate, act_limit), u = clamp(up, +-act_limit)
+    float act_alpha, act_limit;
     int out_f32;      // output element type
     int ldo;          // row stride of the output in elements
     long long split_stride;   // elements between the partial results of two splits (0: no split)
@@ -143,6 +145,14 @@ struct Params {
 // and division (a few units in the last place of float32, far below that rounding) instead of the
 // library's, which cost the epilogue of a 64-token tile more than its loads from tensor memory.
 __device__ __forceinline__ float silu_mul_fast(float gate, float up) { return __fdividef(gate, 1.0f + __expf(-gate)) * up; }
+// the activation of a pair (gate, up): silu(gate) * up, or the clamped form of epilogue 3
+__device__ __forceinline__ float gated_act(const Params &p, float gate, float up) {
+    if (p.swiglu == 3) {
+        const float g = fminf(gate, p.act_limit), u = fminf(fmaxf(up, -p.act_limit), p.act_limit);
+        return __fdividef(g, 1.0f + __expf(-p.act_alpha * g)) * (u + 1.0f);
+    }
+    return silu_mul_fast(gate, up);
+}
 // relu(y)^2, the activation of a dense feed-forward, for the epilogue that applies it in place of a pass of its own
 __device__ __forceinline__ float relu_sq(float y) { const float r = fmaxf(y, 0.f); return r * r; }
 
@@ -158,12 +168,12 @@ __device__ __forceinline__ void store_run(const Params &p, int a_row, int f0, co
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = relu_sq(v[j]);
         }
-        if (p.swiglu == 1) {
+        if (p.swiglu == 1 || p.swiglu == 3) {
             // columns 2j and 2j+1 are the gate and the up of feature (f0 / 2) + j
             const size_t o = (size_t)a_row * p.ldo + (f0 >> 1);
             float act[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) act[j] = silu_mul_fast(v[2 * j], v[2 * j + 1]);
+            for (int j = 0; j < 8; ++j) act[j] = gated_act(p, v[2 * j], v[2 * j + 1]);
             if (f0 + 16 <= p.rows_b && (p.ldo & 7) == 0 && !f32) {
                 uint32_t h[4];
 #pragma unroll
@@ -220,7 +230,7 @@ __device__ __forceinline__ void store_run_transposed(const Params &p, int a_row,
                                                      __nv_bfloat16 *out_h, bool f32) {
     const bool row_ok = a_row < p.rows_a;
     const float b = (p.bias && row_ok) ? p.bias[a_row] : 0.f;
-    if (p.swiglu == 1) {
+    if (p.swiglu == 1 || p.swiglu == 3) {
         // Lanes 2i and 2i+1 hold the gate and the up row of one feature.  Of every two tokens the
         // even lane finishes the first and the odd lane the second: one exchange for two tokens
         // (the even lane gives its gate of the second token, the odd lane its up of the first),
@@ -232,7 +242,7 @@ __device__ __forceinline__ void store_run_transposed(const Params &p, int a_row,
             const float got = __shfl_xor_sync(0xffffffffu, even ? v1 : v0, 1);
             const int token = token0 + j + (even ? 0 : 1);
             if (row_ok && token < p.rows_b) {
-                const float act = even ? silu_mul_fast(v0, got) : silu_mul_fast(got, v1);
+                const float act = even ? gated_act(p, v0, got) : gated_act(p, got, v1);
                 const size_t o = (size_t)token * p.ldo + (a_row >> 1);
                 if (f32) out_f[o] = act;
                 else out_h[o] = __float2bfloat16_rn(act);
@@ -928,16 +938,18 @@ LGML_API long long lgml_gemm_tcgen05_scratch_floats(int M, int N, int n_splits) 
 // y bfloat16 or float32 with row stride ldy.  n_splits > 1 cuts K and needs `scratch`.
 // swiglu = 1: the rows of w come in (gate, up) pairs and y[M, N / 2] = silu(gate) * up (no K split then);
 // swiglu = 2: y = relu(x . w^T + bias)^2 (no K split either).
+// swiglu = 3: pairs as for 1 and y = g sigmoid(act_alpha g) (u + 1), g = min(gate, act_limit), u = clamp(up, +-act_limit).
 // reduce = 0 with n_splits > 1 leaves the partial sums [n_splits, M, N] in scratch for the next
 // kernel to add (bias is then not applied).
-LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, void *y, int y_f32, int M, int N, int K, int ldx,
-                               int ldw, int ldy, int n_splits, float *scratch, int swiglu, int reduce, int *status,
-                               cudaStream_t stream) {
+static int gemm_tcgen05_run(const void *x, const void *w, const float *bias, void *y, int y_f32, int M, int N, int K, int ldx, int ldw, int ldy,
+                            int n_splits, float *scratch, int swiglu, float act_alpha, float act_limit, int reduce, int *status,
+                            cudaStream_t stream) {
     LGML_REQUIRE(M >= 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
-    LGML_REQUIRE(swiglu >= 0 && swiglu <= 2, "gemm_tcgen05: unknown epilogue %d", swiglu);
-    LGML_REQUIRE(ldx >= K && ldw >= K && ldy >= (swiglu == 1 ? N / 2 : N), "gemm_tcgen05: a leading dimension is smaller than its row");
+    LGML_REQUIRE(swiglu >= 0 && swiglu <= 3, "gemm_tcgen05: unknown epilogue %d", swiglu);
+    const bool paired = swiglu == 1 || swiglu == 3;
+    LGML_REQUIRE(ldx >= K && ldw >= K && ldy >= (paired ? N / 2 : N), "gemm_tcgen05: a leading dimension is smaller than its row");
     LGML_REQUIRE(!swiglu || n_splits == 1, "gemm_tcgen05: an epilogue with an activation takes no K split");
-    LGML_REQUIRE(swiglu != 1 || N % 2 == 0, "gemm_tcgen05: the gated epilogue needs an even N");
+    LGML_REQUIRE(!paired || N % 2 == 0, "gemm_tcgen05: the gated epilogue needs an even N");
     LGML_REQUIRE(ldx % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: row strides (%d, %d) must be multiples of 8 elements (16 bytes) for TMA", ldx, ldw);
     LGML_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned for TMA");
     LGML_REQUIRE(n_splits >= 1 && n_splits <= 64, "gemm_tcgen05: bad split count %d", n_splits);
@@ -955,6 +967,7 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
     p.bias = n_splits > 1 ? nullptr : bias;
     p.status = status;
     p.swiglu = swiglu;
+    p.act_alpha = act_alpha, p.act_limit = act_limit;
     CUtensorMap ma, mb;
     int rc;
     dim3 grid;
@@ -1042,4 +1055,17 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
         rc = lgml_launch_status("gemm_tcgen05 split reduce");
     }
     return rc;
+}
+
+LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, void *y, int y_f32, int M, int N, int K, int ldx,
+                               int ldw, int ldy, int n_splits, float *scratch, int swiglu, int reduce, int *status,
+                               cudaStream_t stream) {
+    LGML_REQUIRE(swiglu >= 0 && swiglu <= 2, "gemm_tcgen05: unknown epilogue %d", swiglu);
+    return gemm_tcgen05_run(x, w, bias, y, y_f32, M, N, K, ldx, ldw, ldy, n_splits, scratch, swiglu, 0.f, 0.f, reduce, status, stream);
+}
+
+// The gated epilogue with the clamped activation (epilogue 3): y[M, N / 2] bfloat16 or float32, no K split.
+LGML_API int lgml_gemm_tcgen05_glu_clamped(const void *x, const void *w, void *y, int y_f32, int M, int N, int K, int ldx, int ldw, int ldy,
+                                           float act_alpha, float act_limit, int *status, cudaStream_t stream) {
+    return gemm_tcgen05_run(x, w, nullptr, y, y_f32, M, N, K, ldx, ldw, ldy, 1, nullptr, 3, act_alpha, act_limit, 1, status, stream);
 }

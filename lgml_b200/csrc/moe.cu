@@ -25,13 +25,27 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const T *__restrict__ h
                                                          int *__restrict__ ids, float *__restrict__ wts, int E, int X, int top) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float z[];        // X logits
+    extern __shared__ __align__(16) float rsm[];        // X logits, then the token's row (E floats, from a 16-byte boundary)
+    float *z = rsm, *hs = rsm + ((X + 3) & ~3);
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const T *row = h + (size_t)t * ldh;
+    for (int k = threadIdx.x; k < E; k += blockDim.x) hs[k] = to_f32(act_load(row + k));
+    __syncthreads();
+    // one order of summation whatever the batch: lane l takes elements 4 l .. 4 l + 3 of every run of 128, then the warp's tree
+    const bool vec = (E % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) & 15) == 0);
     for (int e = warp; e < X; e += n_warps) {
+        const float *w = wr + (size_t)e * E;
         float dot = 0.f;
-        for (int k = lane; k < E; k += 32) dot = fmaf(to_f32(act_load(row + k)), wr[(size_t)e * E + k], dot);
+        if (vec) {
+#pragma unroll 4
+            for (int k = lane * 4; k < E; k += 128) {
+                const float4 a = *reinterpret_cast<const float4 *>(hs + k), b = __ldg(reinterpret_cast<const float4 *>(w + k));
+                dot = fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, fmaf(a.w, b.w, dot))));
+            }
+        } else {
+            for (int k = lane; k < E; k += 32) dot = fmaf(hs[k], w[k], dot);
+        }
         dot = warp_sum(dot);
         if (lane == 0) z[e] = dot + (br ? br[e] : 0.f);
     }
@@ -81,13 +95,28 @@ __global__ void __launch_bounds__(GU_WARPS * 32) moe_gate_up_kernel(const T *__r
     e = e < 0 ? 0 : (e >= X ? X - 1 : e);
     __syncthreads();
     const int f0 = (blockIdx.y * GU_WARPS + warp) * GU_PER_WARP;
+    const bool vec = sizeof(T) == 2 && (E % 8 == 0) && ((reinterpret_cast<uintptr_t>(wg) | reinterpret_cast<uintptr_t>(wu)) & 15) == 0;
     for (int f = f0; f < f0 + GU_PER_WARP && f < F; ++f) {
         const T *g_row = wg + ((size_t)e * F + f) * E, *u_row = wu + ((size_t)e * F + f) * E;
         float g = 0.f, u = 0.f;
-        for (int k = lane; k < E; k += 32) {
-            const float x = hs[k];
-            g = fmaf(x, to_f32(g_row[k]), g);
-            u = fmaf(x, to_f32(u_row[k]), u);
+        if (vec) {
+#pragma unroll 2
+            for (int k = lane * 8; k < E; k += 256) {
+                const uint4 rg = __ldg(reinterpret_cast<const uint4 *>(g_row + k)), ru = __ldg(reinterpret_cast<const uint4 *>(u_row + k));
+                const __nv_bfloat162 *pg = reinterpret_cast<const __nv_bfloat162 *>(&rg), *pu = reinterpret_cast<const __nv_bfloat162 *>(&ru);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 a = __bfloat1622float2(pg[i]), b = __bfloat1622float2(pu[i]);
+                    g = fmaf(hs[k + 2 * i], a.x, fmaf(hs[k + 2 * i + 1], a.y, g));
+                    u = fmaf(hs[k + 2 * i], b.x, fmaf(hs[k + 2 * i + 1], b.y, u));
+                }
+            }
+        } else {
+            for (int k = lane; k < E; k += 32) {
+                const float x = hs[k];
+                g = fmaf(x, to_f32(g_row[k]), g);
+                u = fmaf(x, to_f32(u_row[k]), u);
+            }
         }
         g = warp_sum(g);
         u = warp_sum(u);
@@ -115,7 +144,20 @@ __global__ void __launch_bounds__(DN_WARPS * 32) moe_down_kernel(const T *__rest
             e = e < 0 ? 0 : (e >= X ? X - 1 : e);
             const T *d_row = wd + ((size_t)e * E + j) * F;
             float dot = 0.f;
-            for (int k = lane; k < F; k += 32) dot = fmaf(as[(size_t)s * F + k], to_f32(d_row[k]), dot);
+            if (sizeof(T) == 2 && (F % 8 == 0) && (reinterpret_cast<uintptr_t>(wd) & 15) == 0) {
+#pragma unroll 2
+                for (int k = lane * 8; k < F; k += 256) {
+                    const uint4 rd = __ldg(reinterpret_cast<const uint4 *>(d_row + k));
+                    const __nv_bfloat162 *pd = reinterpret_cast<const __nv_bfloat162 *>(&rd);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 a = __bfloat1622float2(pd[i]);
+                        dot = fmaf(as[(size_t)s * F + k + 2 * i], a.x, fmaf(as[(size_t)s * F + k + 2 * i + 1], a.y, dot));
+                    }
+                }
+            } else {
+                for (int k = lane; k < F; k += 32) dot = fmaf(as[(size_t)s * F + k], to_f32(d_row[k]), dot);
+            }
             total = fmaf(act_load(wts + (size_t)t * top + s), warp_sum(dot), total);
         }
         if (lane == 0) out[(size_t)t * E + j] = total;
@@ -138,7 +180,8 @@ LGML_API int lgml_moe_router(const void *h, int dtype, int ldh, const float *wr,
     LGML_REQUIRE(n_tokens >= 0 && E > 0 && X > 0 && top > 0 && top <= X, "moe_router: bad sizes (%d experts, %d chosen)", X, top);
     LGML_REQUIRE(X <= 8192, "moe_router: at most 8192 experts");
     if (n_tokens == 0) return 0;
-    const size_t smem = sizeof(float) * (size_t)X;
+    const size_t smem = sizeof(float) * ((size_t)((X + 3) & ~3) + (size_t)E);
+    LGML_REQUIRE(smem <= 48 * 1024, "moe_router: %d experts and rows of %d do not fit shared memory", X, E);
     if (dtype == LGML_F32)
         lgml_launch(moe_router_kernel<float>, n_tokens, 128, smem, stream, (const float *)h, ldh, wr, br, ids, wts, E, X, top);
     else if (dtype == LGML_BF16)
@@ -178,21 +221,21 @@ LGML_API int lgml_moe_experts_rows(const void *h, int dtype, int ldh, const int 
 
 // ---------------------------------------------------------------------------------------------
 // The grouped form, bfloat16, for many tokens: the (token, chosen expert) rows are sorted by expert,
-// cut into tiles of 64 rows of one expert, and every tile is a product on tensor cores (mma.sync
+// cut into tiles of 128 rows of one expert, and every tile is a product on tensor cores (mma.sync
 // m16n8k16, float32 accumulation) against that expert's matrices, which are then read once per tile
 // and not once per row.
 //   moe_group        counts the rows per expert, lists them expert by expert and writes the tiles
 //                    (expert, first row of the list, rows); one block, no host in the loop, so the
 //                    step stays a fixed sequence of launches whatever the router chose
-//   moe_tile_product C[64 rows, 64 columns] of a tile: MODE 0 gathers the tokens' rows of h, takes 32
-//                    gate and 32 up features at once and writes silu(gate) * up; MODE 1 reads the
+//   moe_tile_product C[128 rows, 128 columns] of a tile: MODE 0 gathers the tokens' rows of h, takes 64
+//                    gate and 64 up features at once and writes silu(gate) * up; MODE 1 reads the
 //                    activations and writes the down product times the row's weight, float32
 //   moe_sum          out[t] = the rows of token t added in the order of its chosen experts
 // A row's result does not depend on where in a tile it lies, so the order in which rows were
 // listed (atomics) does not show in the output.
 // ---------------------------------------------------------------------------------------------
 namespace {
-constexpr int G_TM = 64, G_TN = 64, G_TK = 32, G_LD = G_TK + 8;
+constexpr int G_TM = 128, G_TN = 128, G_TK = 32, G_LD = G_TK + 8;
 
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int *__restrict__ ids, int n_rows, int X, int *__restrict__ rows,
                                                          int *__restrict__ tiles, int *__restrict__ n_tiles, int max_tiles) {
@@ -250,25 +293,30 @@ __device__ __forceinline__ void g_cp16(void *dst, const void *src, bool valid) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(g_smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
 }
 
-// MODE 0: a = h (rows gathered by token), b = 32 rows of w0[e] (gate) then 32 of w1[e] (up) from feature 32 blockIdx.y on,
-//         out0 = act [n_rows, N] bfloat16.  K = E, N = F.
-// MODE 1: a = act rows, b = 64 rows of w0[e] (down) from column 64 blockIdx.y on, out1 = y [n_rows, N] float32, times wts[row].
+// MODE 0: a = h (rows gathered by token), b = 64 gate rows of w0[e] and the 64 up rows of w1[e] of the same features, from feature
+//         64 blockIdx.y on (each of the two warp columns gets 32 gate and its 32 up features), out0 = act [n_rows, N] bfloat16.
+//         K = E, N = F.
+// MODE 1: a = act rows, b = 128 rows of w0[e] (down) from column 128 blockIdx.y on, out1 = y [n_rows, N] float32, times wts[row].
 //         K = F, N = E.
+// Eight warps, four down the rows and two across the columns: a warp owns 32 rows x 64 columns.  Three stages of cp.async.
+constexpr int G_STAGES = 3;
+constexpr int G_STAGE_ELEMS = (G_TM + G_TN) * G_LD;
 template <int MODE>
-__global__ void __launch_bounds__(128) moe_tile_product_kernel(const __nv_bfloat16 *__restrict__ a, int lda, const int *__restrict__ rows,
+__global__ void __launch_bounds__(256) moe_tile_product_kernel(const __nv_bfloat16 *__restrict__ a, int lda, const int *__restrict__ rows,
                                                                const int *__restrict__ tiles, const int *__restrict__ n_tiles,
                                                                const __nv_bfloat16 *__restrict__ w0, const __nv_bfloat16 *__restrict__ w1,
                                                                const float *__restrict__ wts, __nv_bfloat16 *__restrict__ out0,
                                                                float *__restrict__ out1, int K, int N, int top) {
     pdl_trigger();
     pdl_wait();
-    __shared__ __align__(16) __nv_bfloat16 As[2][G_TM * G_LD];
-    __shared__ __align__(16) __nv_bfloat16 Bs[2][G_TN * G_LD];
-    __shared__ int row_of[G_TM];
+    extern __shared__ __align__(16) uint8_t g_raw[];
+    __nv_bfloat16 *stages = reinterpret_cast<__nv_bfloat16 *>(g_raw);
+    int *row_of = reinterpret_cast<int *>(stages + G_STAGES * G_STAGE_ELEMS);
     const int tile = blockIdx.x;
     if (tile >= act_load(n_tiles)) return;
     const int e = act_load(tiles + tile * 3), r0 = act_load(tiles + tile * 3 + 1), n_r = act_load(tiles + tile * 3 + 2);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wm = warp & 3, wn = warp >> 2;
     const int mat = lane >> 3, mrow = lane & 7;
     if (threadIdx.x < G_TM) row_of[threadIdx.x] = threadIdx.x < n_r ? act_load(rows + r0 + threadIdx.x) : -1;
     __syncthreads();
@@ -277,81 +325,94 @@ __global__ void __launch_bounds__(128) moe_tile_product_kernel(const __nv_bfloat
 
     auto issue = [&](int kt, int buf) {
         const int k0 = kt * G_TK;
-        for (int c = threadIdx.x; c < G_TM * (G_TK / 8); c += 128) {
+        __nv_bfloat16 *As = stages + (size_t)buf * G_STAGE_ELEMS, *Bs = As + G_TM * G_LD;
+        for (int c = threadIdx.x; c < G_TM * (G_TK / 8); c += 256) {
             const int r = c / (G_TK / 8), col = (c - r * (G_TK / 8)) * 8;
             const int row = row_of[r];
             const bool ok = row >= 0 && k0 + col < K;
             const size_t src_row = MODE == 0 ? (size_t)(row >= 0 ? row / top : 0) : (size_t)(row >= 0 ? row : 0);
-            g_cp16(&As[buf][r * G_LD + col], a + src_row * lda + (ok ? k0 + col : 0), ok);
+            g_cp16(As + r * G_LD + col, a + src_row * lda + (ok ? k0 + col : 0), ok);
         }
-        for (int c = threadIdx.x; c < G_TN * (G_TK / 8); c += 128) {
+        for (int c = threadIdx.x; c < G_TN * (G_TK / 8); c += 256) {
             const int r = c / (G_TK / 8), col = (c - r * (G_TK / 8)) * 8;
             const __nv_bfloat16 *base;
             int n;
             if (MODE == 0) {
-                n = c0 + (r % HALF);
-                base = (r < HALF ? w0 : w1) + ((size_t)e * N + (n < N ? n : 0)) * K;
+                const int half = r / 64, rr = r % 64;              // the warp column, and gate (rr < 32) or up
+                n = c0 + half * 32 + (rr & 31);
+                base = (rr < 32 ? w0 : w1) + ((size_t)e * N + (n < N ? n : 0)) * K;
             } else {
                 n = c0 + r;
                 base = w0 + ((size_t)e * N + (n < N ? n : 0)) * K;
             }
             const bool ok = n < N && k0 + col < K;
-            g_cp16(&Bs[buf][r * G_LD + col], base + (ok ? k0 + col : 0), ok);
+            g_cp16(Bs + r * G_LD + col, base + (ok ? k0 + col : 0), ok);
         }
     };
-    float acc[8][4];
+    float acc[2][8][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[m][i][0] = acc[m][i][1] = acc[m][i][2] = acc[m][i][3] = 0.f;
     const int n_kt = (K + G_TK - 1) / G_TK;
-    issue(0, 0);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    for (int kt = 0; kt < n_kt; ++kt) {
-        const int buf = kt & 1;
-        if (kt + 1 < n_kt) issue(kt + 1, buf ^ 1);
+#pragma unroll
+    for (int st = 0; st < G_STAGES - 1; ++st) {
+        if (st < n_kt) issue(st, st);
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-        __syncthreads();
+    }
+    for (int kt = 0; kt < n_kt; ++kt) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(G_STAGES - 2) : "memory");
+        __syncthreads();            // stage kt has landed for everyone, and everyone is done with the buffer refilled next
+        if (kt + G_STAGES - 1 < n_kt) issue(kt + G_STAGES - 1, (kt + G_STAGES - 1) % G_STAGES);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const __nv_bfloat16 *As = stages + (size_t)(kt % G_STAGES) * G_STAGE_ELEMS, *Bs = As + G_TM * G_LD;
 #pragma unroll
         for (int ks = 0; ks < G_TK / 16; ++ks) {
-            uint32_t af[4];
-            g_ldmatrix_x4(af, &As[buf][(warp * 16 + (mat & 1) * 8 + mrow) * G_LD + ks * 16 + (mat >> 1) * 8]);
+            uint32_t af[2][4];
+#pragma unroll
+            for (int m = 0; m < 2; ++m)
+                g_ldmatrix_x4(af[m], As + (wm * 32 + m * 16 + (mat & 1) * 8 + mrow) * G_LD + ks * 16 + (mat >> 1) * 8);
 #pragma unroll
             for (int np = 0; np < 4; ++np) {
-                uint32_t b[4];
-                g_ldmatrix_x4(b, &Bs[buf][(np * 16 + (mat >> 1) * 8 + mrow) * G_LD + ks * 16 + (mat & 1) * 8]);
-                g_mma_bf16(acc[2 * np], af, b[0], b[1]);
-                g_mma_bf16(acc[2 * np + 1], af, b[2], b[3]);
+                uint32_t bq[4];
+                g_ldmatrix_x4(bq, Bs + (wn * 64 + np * 16 + (mat >> 1) * 8 + mrow) * G_LD + ks * 16 + (mat & 1) * 8);
+#pragma unroll
+                for (int m = 0; m < 2; ++m) {
+                    g_mma_bf16(acc[m][2 * np], af[m], bq[0], bq[1]);
+                    g_mma_bf16(acc[m][2 * np + 1], af[m], bq[2], bq[3]);
+                }
             }
         }
-        __syncthreads();            // the buffer is free for the copy after next
     }
-    // rows lane / 4 and + 8 of the warp's 16; columns 8 nt + (lane % 4) * 2 and + 1
+    // rows lane / 4 and + 8 of each of the warp's two blocks of 16; columns 8 nt + (lane % 4) * 2 and + 1 of the warp's 64
 #pragma unroll
-    for (int rr = 0; rr < 2; ++rr) {
-        const int r = warp * 16 + (lane >> 2) + rr * 8;
-        const int row = row_of[r];
-        if (row < 0) continue;
-        if (MODE == 0) {
+    for (int m = 0; m < 2; ++m)
 #pragma unroll
-            for (int nt = 0; nt < 4; ++nt)
+        for (int rr = 0; rr < 2; ++rr) {
+            const int r = wm * 32 + m * 16 + (lane >> 2) + rr * 8;
+            const int row = row_of[r];
+            if (row < 0) continue;
+            if (MODE == 0) {
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int f = c0 + nt * 8 + (lane & 3) * 2 + i;
-                    if (f >= N) continue;
-                    const float g = acc[nt][rr * 2 + i], u = acc[nt + 4][rr * 2 + i];
-                    out0[(size_t)row * N + f] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
-                }
-        } else {
-            const float w = act_load(wts + row);
+                for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
+                    for (int i = 0; i < 2; ++i) {
+                        const int f = c0 + wn * 32 + nt * 8 + (lane & 3) * 2 + i;
+                        if (f >= N) continue;
+                        const float g = acc[m][nt][rr * 2 + i], u = acc[m][nt + 4][rr * 2 + i];
+                        out0[(size_t)row * N + f] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+                    }
+            } else {
+                const float w = act_load(wts + row);
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int j = c0 + nt * 8 + (lane & 3) * 2 + i;
-                    if (j < N) out1[(size_t)row * N + j] = acc[nt][rr * 2 + i] * w;
-                }
+                for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        const int j = c0 + wn * 64 + nt * 8 + (lane & 3) * 2 + i;
+                        if (j < N) out1[(size_t)row * N + j] = acc[m][nt][rr * 2 + i] * w;
+                    }
+            }
         }
-    }
 }
 
 __global__ void __launch_bounds__(256) moe_sum_kernel(const float *__restrict__ y, float *__restrict__ out, int n_tokens, int E, int top) {
@@ -385,10 +446,12 @@ LGML_API int lgml_moe_experts_grouped(const void *h, int ldh, const int *ids, co
     lgml_launch(moe_group_kernel, 1, 1024, sizeof(int) * 4 * (size_t)X, stream, ids, n_rows, X, rows, tiles, n_tiles, max_tiles);
     dim3 g0(max_tiles, (F + G_TN / 2 - 1) / (G_TN / 2)), g1(max_tiles, (E + G_TN - 1) / G_TN);
     LGML_REQUIRE(g0.y <= 65535 && g1.y <= 65535, "moe_experts_grouped: too many columns");
-    lgml_launch(moe_tile_product_kernel<0>, g0, 128, 0, stream, (const __nv_bfloat16 *)h, ldh, (const int *)rows, (const int *)tiles,
+    const size_t smem = (size_t)G_STAGES * G_STAGE_ELEMS * 2 + sizeof(int) * G_TM;
+    if (need_smem(moe_tile_product_kernel<0>, smem, "moe_experts_grouped") || need_smem(moe_tile_product_kernel<1>, smem, "moe_experts_grouped")) return -1;
+    lgml_launch(moe_tile_product_kernel<0>, g0, 256, smem, stream, (const __nv_bfloat16 *)h, ldh, (const int *)rows, (const int *)tiles,
                 (const int *)n_tiles, (const __nv_bfloat16 *)wg, (const __nv_bfloat16 *)wu, (const float *)nullptr, (__nv_bfloat16 *)act,
                 (float *)nullptr, E, F, top);
-    lgml_launch(moe_tile_product_kernel<1>, g1, 128, 0, stream, (const __nv_bfloat16 *)act, F, (const int *)rows, (const int *)tiles,
+    lgml_launch(moe_tile_product_kernel<1>, g1, 256, smem, stream, (const __nv_bfloat16 *)act, F, (const int *)rows, (const int *)tiles,
                 (const int *)n_tiles, (const __nv_bfloat16 *)wd, (const __nv_bfloat16 *)nullptr, wts, (__nv_bfloat16 *)nullptr, y, F, E, top);
     const size_t total = (size_t)n_tokens * E;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);

@@ -863,7 +863,7 @@ def moe_experts_rows(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_ga
     return out
 
 
-MOE_TILE_ROWS = 64
+MOE_TILE_ROWS = 128
 
 
 def moe_grouped_supports(h: torch.Tensor, w_gate: torch.Tensor) -> bool:
@@ -874,7 +874,7 @@ def moe_grouped_supports(h: torch.Tensor, w_gate: torch.Tensor) -> bool:
 
 def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
     """``moe_experts_rows`` for many tokens, bfloat16: the (token, chosen expert) rows sorted by expert on
-    the device and cut into tiles of 64 rows of one expert, each tile a product on tensor cores; float32
+    the device and cut into tiles of 128 rows of one expert, each tile a product on tensor cores; float32
     [tokens, E].  No host value is read: the launches are the same whatever the router chose."""
     _need(h, "experts' input", torch.bfloat16, 2)
     for t, what in ((w_gate, "gate"), (w_up, "up"), (w_down, "down")):
@@ -1228,7 +1228,27 @@ def gemm_bf16_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, bias_pairs: Optiona
     return gemm_tcgen05(x, w_pairs, out, bias_pairs, status, swiglu=True)
 
 
-GLU_CLAMPED_FUSED = False     # the clamped gated activation in the product's epilogue (not built: the two-kernel form runs)
+GLU_CLAMPED_FUSED = os.environ.get("LGML_GLU_FUSED") != "0"     # the clamped gated activation in the product's epilogue
+
+
+def gemm_bf16_glu_clamped(x: torch.Tensor, w_pairs: torch.Tensor, alpha: float, limit: float, status: torch.Tensor) -> torch.Tensor:
+    """act[M, F] = g sigmoid(alpha g) (u + 1) with g = min(x . gate^T, limit), u = clamp(x . up^T, -limit, limit), in one
+    kernel; ``w_pairs`` [2F, K] holds the gate and up rows of each feature next to each other (gate first)."""
+    _need(x, "gemm input", torch.bfloat16, 2)
+    _need(w_pairs, "gemm weight", torch.bfloat16, 2)
+    ldx, ldw = _rows_contiguous(x, "gemm input"), _rows_contiguous(w_pairs, "gemm weight")
+    M, K = x.shape
+    N = w_pairs.shape[0]
+    if w_pairs.shape[1] != K or N % 2:
+        raise KernelError(f"gemm_bf16_glu_clamped: shapes disagree: x {tuple(x.shape)}, w {tuple(w_pairs.shape)}")
+    out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+    if M == 0:
+        return out
+    fn = _fn("gemm_tcgen05", "lgml_gemm_tcgen05_glu_clamped", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                               c_float, c_void_p, c_void_p])
+    _check("gemm_tcgen05", fn(_ptr(x), _ptr(w_pairs), _ptr(out), 0, M, N, K, ldx, ldw, out.stride(0), float(alpha), float(limit), _ptr(status),
+                              _stream()), "gemm_tcgen05_glu_clamped")
+    return out
 
 
 def gemm_bf16_relu_sq(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], status: torch.Tensor) -> torch.Tensor:

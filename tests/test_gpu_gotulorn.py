@@ -26,7 +26,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 ROOT = Path(__file__).resolve().parent.parent
 F64 = torch.float64
-TOL = {"float32": dict(atol=3e-5, rtol=2e-4), "bfloat16": dict(atol=3e-2, rtol=5e-2)}
+TOL = {"float32": dict(atol=3e-5, rtol=2e-4), "bfloat16": dict(atol=3e-2, rtol=8e-2)}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -269,6 +269,26 @@ def test_dynamic_tanh_and_clamped_gate(dtype):
     want = g * torch.sigmoid(1.702 * g) * (u + 1)
     assert float((act.double().cpu() - want).abs().max()) < (1e-5 if dtype == torch.float32 else 3e-2)
     assert float((gu.double().abs() > 1.5).double().mean()) > 0.3          # the clamp was at work
+
+
+@pytest.mark.parametrize("M", [1, 7, 64, 65, 300])
+def test_clamped_gate_in_the_products_epilogue(M):
+    """The gate|up product with the clamped activation in its epilogue against the plain formula; both
+    orientations of the product's tile and the pairs of CTAs (1 to 300 tokens)."""
+    from lgml_b200 import ops
+
+    torch.manual_seed(9 + M)
+    K, F = 192, 136
+    x = torch.randn(M, K, dtype=F64).to(torch.bfloat16)
+    wg, wu = (torch.randn(F, K, dtype=F64) * 0.2).to(torch.bfloat16), (torch.randn(F, K, dtype=F64) * 0.2).to(torch.bfloat16)
+    pairs = torch.stack([wg, wu], dim=1).reshape(2 * F, K).contiguous().to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    act = ops.gemm_bf16_glu_clamped(x.to(DEV), pairs, 1.702, 1.5, status)
+    assert int(status.item()) == 0
+    g, u = (x.double() @ wg.double().T).clamp(max=1.5), (x.double() @ wu.double().T).clamp(-1.5, 1.5)
+    want = g * torch.sigmoid(1.702 * g) * (u + 1)
+    assert float((act.double().cpu() - want).abs().max()) < 3e-2
+    assert float(((x.double() @ wu.double().T).abs() > 1.5).double().mean()) > 0.2          # the clamp was at work
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
