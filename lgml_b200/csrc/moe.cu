@@ -80,14 +80,37 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const T *__restrict__ h
     for (int s = lane; s < top; s += 32) wts[(size_t)t * top + s] *= inv;
 }
 
-// act[(t top + s), f] = silu(Wg[e] h_t)[f] * (Wu[e] h_t)[f], e = ids[t, s]
-constexpr int GU_WARPS = 4, GU_PER_WARP = 8;
+// dot products of `NF` weight rows (bfloat16, 16-byte loads) with one float32 vector in shared memory: the loads of all rows of a
+// step go out before any is used.  Lane l takes elements 8 l .. 8 l + 7 of every run of 256; the warp's tree adds the lanes.
+template <int NF>
+__device__ __forceinline__ void rows_dot_bf16(const __nv_bfloat16 *const (&rows)[NF], const float *x, int K, int lane, float (&out)[NF]) {
+#pragma unroll
+    for (int i = 0; i < NF; ++i) out[i] = 0.f;
+    for (int k = lane * 8; k < K; k += 256) {
+        uint4 raw[NF];
+#pragma unroll
+        for (int i = 0; i < NF; ++i) raw[i] = __ldg(reinterpret_cast<const uint4 *>(rows[i] + k));
+        const float4 xa = *reinterpret_cast<const float4 *>(x + k), xb = *reinterpret_cast<const float4 *>(x + k + 4);
+#pragma unroll
+        for (int i = 0; i < NF; ++i) {
+            const __nv_bfloat162 *pr = reinterpret_cast<const __nv_bfloat162 *>(&raw[i]);
+            const float2 a = __bfloat1622float2(pr[0]), b = __bfloat1622float2(pr[1]), c = __bfloat1622float2(pr[2]), d = __bfloat1622float2(pr[3]);
+            out[i] = fmaf(xa.x, a.x, fmaf(xa.y, a.y, fmaf(xa.z, b.x, fmaf(xa.w, b.y, out[i]))));
+            out[i] = fmaf(xb.x, c.x, fmaf(xb.y, c.y, fmaf(xb.z, d.x, fmaf(xb.w, d.y, out[i]))));
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NF; ++i) out[i] = warp_sum(out[i]);
+}
+
+// act[(t top + s), f] = silu(Wg[e] h_t)[f] * (Wu[e] h_t)[f], e = ids[t, s].  A warp takes GU_PER_WARP features at once.
+constexpr int GU_WARPS = 4, GU_PER_WARP = 4;
 template <typename T>
 __global__ void __launch_bounds__(GU_WARPS * 32) moe_gate_up_kernel(const T *__restrict__ h, int ldh, const int *__restrict__ ids, const T *__restrict__ wg,
                                                                     const T *__restrict__ wu, T *__restrict__ act, int E, int F, int X, int top) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float hs[];       // the token's row
+    extern __shared__ __align__(16) float hs[];       // the token's row
     const int row = blockIdx.x, t = row / top;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int k = threadIdx.x; k < E; k += blockDim.x) hs[k] = to_f32(act_load(h + (size_t)t * ldh + k));
@@ -95,28 +118,30 @@ __global__ void __launch_bounds__(GU_WARPS * 32) moe_gate_up_kernel(const T *__r
     e = e < 0 ? 0 : (e >= X ? X - 1 : e);
     __syncthreads();
     const int f0 = (blockIdx.y * GU_WARPS + warp) * GU_PER_WARP;
-    const bool vec = sizeof(T) == 2 && (E % 8 == 0) && ((reinterpret_cast<uintptr_t>(wg) | reinterpret_cast<uintptr_t>(wu)) & 15) == 0;
+    if (f0 >= F) return;
+    if (sizeof(T) == 2 && (E % 8 == 0) && ((reinterpret_cast<uintptr_t>(wg) | reinterpret_cast<uintptr_t>(wu)) & 15) == 0) {
+        const __nv_bfloat16 *rows[2 * GU_PER_WARP];
+#pragma unroll
+        for (int i = 0; i < GU_PER_WARP; ++i) {
+            const int f = min(f0 + i, F - 1);
+            rows[i] = reinterpret_cast<const __nv_bfloat16 *>(wg) + ((size_t)e * F + f) * E;
+            rows[GU_PER_WARP + i] = reinterpret_cast<const __nv_bfloat16 *>(wu) + ((size_t)e * F + f) * E;
+        }
+        float r[2 * GU_PER_WARP];
+        rows_dot_bf16<2 * GU_PER_WARP>(rows, hs, E, lane, r);
+        if (lane == 0)
+#pragma unroll
+            for (int i = 0; i < GU_PER_WARP; ++i)
+                if (f0 + i < F) act[(size_t)row * F + f0 + i] = from_f32<T>(r[i] / (1.0f + expf(-r[i])) * r[GU_PER_WARP + i]);
+        return;
+    }
     for (int f = f0; f < f0 + GU_PER_WARP && f < F; ++f) {
         const T *g_row = wg + ((size_t)e * F + f) * E, *u_row = wu + ((size_t)e * F + f) * E;
         float g = 0.f, u = 0.f;
-        if (vec) {
-#pragma unroll 2
-            for (int k = lane * 8; k < E; k += 256) {
-                const uint4 rg = __ldg(reinterpret_cast<const uint4 *>(g_row + k)), ru = __ldg(reinterpret_cast<const uint4 *>(u_row + k));
-                const __nv_bfloat162 *pg = reinterpret_cast<const __nv_bfloat162 *>(&rg), *pu = reinterpret_cast<const __nv_bfloat162 *>(&ru);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 a = __bfloat1622float2(pg[i]), b = __bfloat1622float2(pu[i]);
-                    g = fmaf(hs[k + 2 * i], a.x, fmaf(hs[k + 2 * i + 1], a.y, g));
-                    u = fmaf(hs[k + 2 * i], b.x, fmaf(hs[k + 2 * i + 1], b.y, u));
-                }
-            }
-        } else {
-            for (int k = lane; k < E; k += 32) {
-                const float x = hs[k];
-                g = fmaf(x, to_f32(g_row[k]), g);
-                u = fmaf(x, to_f32(u_row[k]), u);
-            }
+        for (int k = lane; k < E; k += 32) {
+            const float x = hs[k];
+            g = fmaf(x, to_f32(g_row[k]), g);
+            u = fmaf(x, to_f32(u_row[k]), u);
         }
         g = warp_sum(g);
         u = warp_sum(u);
@@ -124,44 +149,51 @@ __global__ void __launch_bounds__(GU_WARPS * 32) moe_gate_up_kernel(const T *__r
     }
 }
 
-// out[t, j] = sum_s wts[t, s] (Wd[ids[t, s]] act[t top + s])[j], float32; the chosen experts in their order
-constexpr int DN_WARPS = 4, DN_PER_WARP = 8;
+// out[t, j] = sum_s wts[t, s] (Wd[ids[t, s]] act[t top + s])[j], float32; the chosen experts in their order.  A warp takes
+// DN_PER_WARP outputs at once.
+constexpr int DN_WARPS = 4, DN_PER_WARP = 4;
 template <typename T>
 __global__ void __launch_bounds__(DN_WARPS * 32) moe_down_kernel(const T *__restrict__ act, const int *__restrict__ ids, const float *__restrict__ wts,
                                                                  const T *__restrict__ wd, float *__restrict__ out, int E, int F, int X, int top) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float as[];       // top rows of F
+    extern __shared__ __align__(16) float as[];       // top rows of F
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int k = threadIdx.x; k < top * F; k += blockDim.x) as[k] = to_f32(act_load(act + (size_t)t * top * F + k));
     __syncthreads();
     const int j0 = (blockIdx.y * DN_WARPS + warp) * DN_PER_WARP;
-    for (int j = j0; j < j0 + DN_PER_WARP && j < E; ++j) {
-        float total = 0.f;
-        for (int s = 0; s < top; ++s) {
-            int e = act_load(ids + (size_t)t * top + s);
-            e = e < 0 ? 0 : (e >= X ? X - 1 : e);
-            const T *d_row = wd + ((size_t)e * E + j) * F;
-            float dot = 0.f;
-            if (sizeof(T) == 2 && (F % 8 == 0) && (reinterpret_cast<uintptr_t>(wd) & 15) == 0) {
-#pragma unroll 2
-                for (int k = lane * 8; k < F; k += 256) {
-                    const uint4 rd = __ldg(reinterpret_cast<const uint4 *>(d_row + k));
-                    const __nv_bfloat162 *pd = reinterpret_cast<const __nv_bfloat162 *>(&rd);
+    if (j0 >= E) return;
+    const bool vec = sizeof(T) == 2 && (F % 8 == 0) && (reinterpret_cast<uintptr_t>(wd) & 15) == 0;
+    float total[DN_PER_WARP];
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 a = __bfloat1622float2(pd[i]);
-                        dot = fmaf(as[(size_t)s * F + k + 2 * i], a.x, fmaf(as[(size_t)s * F + k + 2 * i + 1], a.y, dot));
-                    }
-                }
-            } else {
+    for (int i = 0; i < DN_PER_WARP; ++i) total[i] = 0.f;
+    for (int s = 0; s < top; ++s) {
+        int e = act_load(ids + (size_t)t * top + s);
+        e = e < 0 ? 0 : (e >= X ? X - 1 : e);
+        const float w = act_load(wts + (size_t)t * top + s);
+        float r[DN_PER_WARP];
+        if (vec) {
+            const __nv_bfloat16 *rows[DN_PER_WARP];
+#pragma unroll
+            for (int i = 0; i < DN_PER_WARP; ++i) rows[i] = reinterpret_cast<const __nv_bfloat16 *>(wd) + ((size_t)e * E + min(j0 + i, E - 1)) * F;
+            rows_dot_bf16<DN_PER_WARP>(rows, as + (size_t)s * F, F, lane, r);
+        } else {
+#pragma unroll
+            for (int i = 0; i < DN_PER_WARP; ++i) {
+                const T *d_row = wd + ((size_t)e * E + min(j0 + i, E - 1)) * F;
+                float dot = 0.f;
                 for (int k = lane; k < F; k += 32) dot = fmaf(as[(size_t)s * F + k], to_f32(d_row[k]), dot);
+                r[i] = warp_sum(dot);
             }
-            total = fmaf(act_load(wts + (size_t)t * top + s), warp_sum(dot), total);
         }
-        if (lane == 0) out[(size_t)t * E + j] = total;
+#pragma unroll
+        for (int i = 0; i < DN_PER_WARP; ++i) total[i] = fmaf(w, r[i], total[i]);
     }
+    if (lane == 0)
+#pragma unroll
+        for (int i = 0; i < DN_PER_WARP; ++i)
+            if (j0 + i < E) out[(size_t)t * E + j0 + i] = total[i];
 }
 
 template <typename K>

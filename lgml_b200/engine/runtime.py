@@ -27,7 +27,7 @@ _STATUS_TEXT = {
 
 AHEAD_BYTES = 24 << 20      # weights asked of L2 ahead, per layer (measured best at 24 to 32 MiB)
 AHEAD_MAX_BATCH = 4         # ... in captured steps of at most this many requests (at 8 the step gets slower)
-MOE_GROUPED_ROWS = 16       # (token, expert) rows of a step from which the experts run as grouped tiles
+MOE_GROUPED_ROWS = 32       # (token, expert) rows of a step from which the experts run as grouped tiles
 MAX_RESULT = 4096     # most sampled rows of a step whose ids travel with the status word
 
 
