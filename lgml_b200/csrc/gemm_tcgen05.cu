@@ -139,6 +139,11 @@ struct Params {
     void *out;        // y, or the float32 partial results
     const float *bias;        // per feature, or null (only when there is no split)
     int *status;
+    // A grouped product (null: none): the rows of A come in tiles of BM rows, tile t of them against the rows
+    // group[3 t] * group_rows_b ... of B (the matrices of several experts stacked); group[3 group_max_tiles] says
+    // how many tiles there are.  The list is written on the device by the kernel ahead, so it is read after the wait.
+    const int *group;
+    int group_max_tiles, group_rows_b;
 };
 
 // silu(gate) * up for the gated epilogue, whose result is rounded to bfloat16: the fast exponential
@@ -291,7 +296,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
     const int kb0 = split * p.kb_per_split;
     const int kb1 = min(kb0 + p.kb_per_split, p.k_blocks);
     const int n_kb = max(kb1 - kb0, 0);
-    const int n_tiles = p.tiles_a * p.tiles_b;
+    const bool grouped = p.group != nullptr;
+    int ta = p.tiles_a;                // tiles along A: fewer in a grouped product, once its tile list is there
+    int n_tiles = ta * p.tiles_b;
     constexpr uint32_t ACC_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
     constexpr uint32_t TMEM_COLS = ACC_COLS * NACC;
     static_assert(TMEM_COLS <= 512, "the accumulators do not fit tensor memory");
@@ -321,8 +328,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
         if (lane == 0) {
             // Weights do not depend on the kernels before this one: fetch them for the first
             // stages at once, then wait for the earlier kernels, then fetch the activations.
+            if (grouped) {          // which weights a tile reads is in the list the kernel ahead wrote: nothing is fetched before the wait
+                pdl_wait();
+                ta = min(p.tiles_a, act_load(p.group + 3 * p.group_max_tiles));
+                n_tiles = ta * p.tiles_b;
+            }
             const int first = blockIdx.x;
-            const int pre = first < n_tiles ? min(n_kb, STAGES) : 0;
+            const int pre = (!grouped && first < n_tiles) ? min(n_kb, STAGES) : 0;
             {
                 const int tile_a = first % p.tiles_a, tile_b = first / p.tiles_a;
                 for (int i = 0; i < pre; ++i) {
@@ -341,7 +353,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
             int it = pre, issued = pre;       // k blocks issued so far, over all tiles of this CTA
             bool ok = true;
             for (int tile = first; tile < n_tiles && ok; tile += gridDim.x) {
-                const int tile_a = tile % p.tiles_a, tile_b = tile / p.tiles_a;
+                const int tile_a = tile % ta, tile_b = tile / ta;
+                const int b_row = tile_b * BN + (grouped ? act_load(p.group + 3 * tile_a) * p.group_rows_b : 0);
                 for (int i = (tile == first ? pre : 0); i < n_kb; ++i, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1, abort_flag, p.status) || *abort_flag) {
@@ -352,7 +365,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
                     uint8_t *b_dst = a_dst + Smem<BN>::A_BYTES;
                     mbar_expect_tx(&full_bar[s], Smem<BN>::STAGE_BYTES);
                     tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, tile_a * BM, &full_bar[s]);
-                    tma_load_2d(b_dst, &map_b, (kb0 + i) * BK, tile_b * BN, &full_bar[s]);
+                    tma_load_2d(b_dst, &map_b, (kb0 + i) * BK, b_row, &full_bar[s]);
                     issued = it + 1;
                 }
             }
@@ -373,6 +386,11 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
             constexpr uint32_t idesc = make_idesc(BM, BN);
             bool ok = true;
             int it = 0, j = 0;
+            if (grouped) {
+                pdl_wait();
+                ta = min(p.tiles_a, act_load(p.group + 3 * p.group_max_tiles));
+                n_tiles = ta * p.tiles_b;
+            }
             for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
                 const int acc = j % NACC;
                 // the epilogue must have drained this accumulator (its use NACC tiles ago)
@@ -407,8 +425,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
         __nv_bfloat16 *out_h = (__nv_bfloat16 *)p.out;
         const bool f32 = p.out_f32 || p.split_stride != 0;
         int j = 0;
+        if (grouped) {
+            ta = min(p.tiles_a, act_load(p.group + 3 * p.group_max_tiles));
+            n_tiles = ta * p.tiles_b;
+        }
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
-        const int tile_a = tile % p.tiles_a, tile_b = tile / p.tiles_a;
+        const int tile_a = tile % ta, tile_b = tile / ta;
         const int acc = j % NACC;
         const uint32_t acc_col = (uint32_t)acc * ACC_COLS;
         const int a_row = tile_a * BM + row;
@@ -968,6 +990,7 @@ static int gemm_tcgen05_run(const void *x, const void *w, const float *bias, voi
     p.status = status;
     p.swiglu = swiglu;
     p.act_alpha = act_alpha, p.act_limit = act_limit;
+    p.group = nullptr, p.group_max_tiles = 0, p.group_rows_b = 0;
     CUtensorMap ma, mb;
     int rc;
     dim3 grid;
@@ -1068,4 +1091,43 @@ LGML_API int lgml_gemm_tcgen05(const void *x, const void *w, const float *bias, 
 LGML_API int lgml_gemm_tcgen05_glu_clamped(const void *x, const void *w, void *y, int y_f32, int M, int N, int K, int ldx, int ldw, int ldy,
                                            float act_alpha, float act_limit, int *status, cudaStream_t stream) {
     return gemm_tcgen05_run(x, w, nullptr, y, y_f32, M, N, K, ldx, ldw, ldy, 1, nullptr, 3, act_alpha, act_limit, 1, status, stream);
+}
+
+// A grouped product: x [max_tiles * 128, K] holds tiles of 128 rows, tile t of them multiplied by the rows
+// group[3 t] * N ... + N - 1 of w [n_groups * N, K] (the matrices of n_groups experts stacked); group[3 max_tiles] is the
+// number of tiles in use, read on the device (the list is written by the kernel ahead).  y [max_tiles * 128, N], or
+// [.., N / 2] with swiglu = 1 (rows of w in (gate, up) pairs, y = silu(gate) * up).  The single-CTA persistent kernel with
+// 128 x 256 tiles; rows of a tile past an expert's last feature are computed from the next expert's rows and not stored.
+LGML_API int lgml_gemm_tcgen05_grouped(const void *x, const void *w, void *y, int y_f32, int max_tiles, int N, int K, int n_groups, int ldy,
+                                       const int *group, int swiglu, int *status, cudaStream_t stream) {
+    LGML_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && n_groups > 0 && group != nullptr, "gemm_tcgen05_grouped: bad sizes");
+    LGML_REQUIRE(swiglu == 0 || swiglu == 1, "gemm_tcgen05_grouped: unknown epilogue %d", swiglu);
+    LGML_REQUIRE(swiglu == 0 || N % 2 == 0, "gemm_tcgen05_grouped: the gated epilogue needs an even N");
+    LGML_REQUIRE(K % 8 == 0, "gemm_tcgen05_grouped: K = %d must be a multiple of 8 elements (16 bytes) for TMA", K);
+    LGML_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tcgen05_grouped: operands must be 16-byte aligned for TMA");
+    LGML_REQUIRE(ldy >= (swiglu ? N / 2 : N), "gemm_tcgen05_grouped: the output's rows are too short");
+    Params p;
+    p.k_blocks = (K + BK - 1) / BK;
+    p.kb_per_split = p.k_blocks;
+    p.out_f32 = y_f32;
+    p.ldo = ldy;
+    p.split_stride = 0;
+    p.out = y;
+    p.bias = nullptr;
+    p.status = status;
+    p.swiglu = swiglu;
+    p.act_alpha = p.act_limit = 0.f;
+    p.transposed = 0;
+    p.rows_a = max_tiles * BM;
+    p.rows_b = N;
+    p.tiles_a = max_tiles;
+    p.tiles_b = (N + 255) / 256;
+    p.group = group, p.group_max_tiles = max_tiles, p.group_rows_b = N;
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = make_map(&ma, x, (long long)max_tiles * BM, K, K, BM))) return rc;
+    if ((rc = make_map(&mb, w, (long long)n_groups * N, K, K, 256))) return rc;
+    const int n_tiles = p.tiles_a * p.tiles_b;
+    dim3 grid(n_tiles < 148 ? n_tiles : 148, 1, 1);
+    return launch<256, 4, 2>(ma, mb, p, grid, stream);
 }

@@ -6,7 +6,8 @@
 //   y      = sum_e w_e W_down[e] (silu(W_gate[e] h) * (W_up[e] h))
 //
 // moe_router writes the chosen experts and their weights, [tokens, top] each.  The experts'
-// matrices lie stacked, [X, F, E] for gate and up and [X, E, F] for down.
+// matrices lie stacked: gate and up as [X, 2 F, E] with the gate row of a feature followed by its up row (the layout
+// whose product has both in one thread's hands), down as [X, E, F].
 //
 // Two forms of the experts' products.  The row form (moe_gate_up, moe_down): a block per (token,
 // chosen expert), a warp per output feature, k in a fixed order; it reads an expert's matrices
@@ -106,8 +107,8 @@ __device__ __forceinline__ void rows_dot_bf16(const __nv_bfloat16 *const (&rows)
 // act[(t top + s), f] = silu(Wg[e] h_t)[f] * (Wu[e] h_t)[f], e = ids[t, s].  A warp takes GU_PER_WARP features at once.
 constexpr int GU_WARPS = 4, GU_PER_WARP = 4;
 template <typename T>
-__global__ void __launch_bounds__(GU_WARPS * 32) moe_gate_up_kernel(const T *__restrict__ h, int ldh, const int *__restrict__ ids, const T *__restrict__ wg,
-                                                                    const T *__restrict__ wu, T *__restrict__ act, int E, int F, int X, int top) {
+__global__ void __launch_bounds__(GU_WARPS * 32) moe_gate_up_kernel(const T *__restrict__ h, int ldh, const int *__restrict__ ids, const T *__restrict__ wgu,
+                                                                    T *__restrict__ act, int E, int F, int X, int top) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float hs[];       // the token's row
@@ -119,13 +120,15 @@ __global__ void __launch_bounds__(GU_WARPS * 32) moe_gate_up_kernel(const T *__r
     __syncthreads();
     const int f0 = (blockIdx.y * GU_WARPS + warp) * GU_PER_WARP;
     if (f0 >= F) return;
-    if (sizeof(T) == 2 && (E % 8 == 0) && ((reinterpret_cast<uintptr_t>(wg) | reinterpret_cast<uintptr_t>(wu)) & 15) == 0) {
+    // expert e's rows: gate of feature f at row 2 f, its up at row 2 f + 1
+    const T *we = wgu + (size_t)e * 2 * F * E;
+    if (sizeof(T) == 2 && (E % 8 == 0) && (reinterpret_cast<uintptr_t>(wgu) & 15) == 0) {
         const __nv_bfloat16 *rows[2 * GU_PER_WARP];
 #pragma unroll
         for (int i = 0; i < GU_PER_WARP; ++i) {
             const int f = min(f0 + i, F - 1);
-            rows[i] = reinterpret_cast<const __nv_bfloat16 *>(wg) + ((size_t)e * F + f) * E;
-            rows[GU_PER_WARP + i] = reinterpret_cast<const __nv_bfloat16 *>(wu) + ((size_t)e * F + f) * E;
+            rows[i] = reinterpret_cast<const __nv_bfloat16 *>(we) + (size_t)(2 * f) * E;
+            rows[GU_PER_WARP + i] = rows[i] + E;
         }
         float r[2 * GU_PER_WARP];
         rows_dot_bf16<2 * GU_PER_WARP>(rows, hs, E, lane, r);
@@ -136,7 +139,7 @@ __global__ void __launch_bounds__(GU_WARPS * 32) moe_gate_up_kernel(const T *__r
         return;
     }
     for (int f = f0; f < f0 + GU_PER_WARP && f < F; ++f) {
-        const T *g_row = wg + ((size_t)e * F + f) * E, *u_row = wu + ((size_t)e * F + f) * E;
+        const T *g_row = we + (size_t)(2 * f) * E, *u_row = g_row + E;
         float g = 0.f, u = 0.f;
         for (int k = lane; k < E; k += 32) {
             const float x = hs[k];
@@ -224,7 +227,7 @@ LGML_API int lgml_moe_router(const void *h, int dtype, int ldh, const float *wr,
 }
 
 // The row form: act [n top, F] in the compute type (scratch of the caller), out float32 [n, E].
-LGML_API int lgml_moe_experts_rows(const void *h, int dtype, int ldh, const int *ids, const float *wts, const void *wg, const void *wu, const void *wd,
+LGML_API int lgml_moe_experts_rows(const void *h, int dtype, int ldh, const int *ids, const float *wts, const void *wgu, const void *wd,
                                    void *act, float *out, int n_tokens, int E, int F, int X, int top, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && E > 0 && F > 0 && X > 0 && top > 0, "moe_experts_rows: bad sizes");
     if (n_tokens == 0) return 0;
@@ -234,15 +237,15 @@ LGML_API int lgml_moe_experts_rows(const void *h, int dtype, int ldh, const int 
     dim3 grid_dn(n_tokens, (E + DN_WARPS * DN_PER_WARP - 1) / (DN_WARPS * DN_PER_WARP));
     if (dtype == LGML_F32) {
         if (need_smem(moe_gate_up_kernel<float>, smem_gu, "moe_experts_rows") || need_smem(moe_down_kernel<float>, smem_dn, "moe_experts_rows")) return -1;
-        lgml_launch(moe_gate_up_kernel<float>, grid_gu, GU_WARPS * 32, smem_gu, stream, (const float *)h, ldh, ids, (const float *)wg, (const float *)wu,
-                    (float *)act, E, F, X, top);
+        lgml_launch(moe_gate_up_kernel<float>, grid_gu, GU_WARPS * 32, smem_gu, stream, (const float *)h, ldh, ids, (const float *)wgu, (float *)act, E, F, X,
+                    top);
         lgml_launch(moe_down_kernel<float>, grid_dn, DN_WARPS * 32, smem_dn, stream, (const float *)act, ids, wts, (const float *)wd, out, E, F, X, top);
     } else if (dtype == LGML_BF16) {
         if (need_smem(moe_gate_up_kernel<__nv_bfloat16>, smem_gu, "moe_experts_rows") ||
             need_smem(moe_down_kernel<__nv_bfloat16>, smem_dn, "moe_experts_rows"))
             return -1;
         lgml_launch(moe_gate_up_kernel<__nv_bfloat16>, grid_gu, GU_WARPS * 32, smem_gu, stream, (const __nv_bfloat16 *)h, ldh, ids,
-                    (const __nv_bfloat16 *)wg, (const __nv_bfloat16 *)wu, (__nv_bfloat16 *)act, E, F, X, top);
+                    (const __nv_bfloat16 *)wgu, (__nv_bfloat16 *)act, E, F, X, top);
         lgml_launch(moe_down_kernel<__nv_bfloat16>, grid_dn, DN_WARPS * 32, smem_dn, stream, (const __nv_bfloat16 *)act, ids, wts,
                     (const __nv_bfloat16 *)wd, out, E, F, X, top);
     } else {
@@ -325,7 +328,7 @@ __device__ __forceinline__ void g_cp16(void *dst, const void *src, bool valid) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(g_smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
 }
 
-// MODE 0: a = h (rows gathered by token), b = 64 gate rows of w0[e] and the 64 up rows of w1[e] of the same features, from feature
+// MODE 0: a = h (rows gathered by token), b = 64 gate rows and the 64 up rows of the same features of w0[e] (pairs), from feature
 //         64 blockIdx.y on (each of the two warp columns gets 32 gate and its 32 up features), out0 = act [n_rows, N] bfloat16.
 //         K = E, N = F.
 // MODE 1: a = act rows, b = 128 rows of w0[e] (down) from column 128 blockIdx.y on, out1 = y [n_rows, N] float32, times wts[row].
@@ -336,8 +339,7 @@ constexpr int G_STAGE_ELEMS = (G_TM + G_TN) * G_LD;
 template <int MODE>
 __global__ void __launch_bounds__(256) moe_tile_product_kernel(const __nv_bfloat16 *__restrict__ a, int lda, const int *__restrict__ rows,
                                                                const int *__restrict__ tiles, const int *__restrict__ n_tiles,
-                                                               const __nv_bfloat16 *__restrict__ w0, const __nv_bfloat16 *__restrict__ w1,
-                                                               const float *__restrict__ wts, __nv_bfloat16 *__restrict__ out0,
+                                                               const __nv_bfloat16 *__restrict__ w0, const float *__restrict__ wts, __nv_bfloat16 *__restrict__ out0,
                                                                float *__restrict__ out1, int K, int N, int top) {
     pdl_trigger();
     pdl_wait();
@@ -372,7 +374,7 @@ __global__ void __launch_bounds__(256) moe_tile_product_kernel(const __nv_bfloat
             if (MODE == 0) {
                 const int half = r / 64, rr = r % 64;              // the warp column, and gate (rr < 32) or up
                 n = c0 + half * 32 + (rr & 31);
-                base = (rr < 32 ? w0 : w1) + ((size_t)e * N + (n < N ? n : 0)) * K;
+                base = w0 + ((size_t)e * 2 * N + 2 * (n < N ? n : 0) + (rr < 32 ? 0 : 1)) * K;      // gate at row 2 n, up at 2 n + 1
             } else {
                 n = c0 + r;
                 base = w0 + ((size_t)e * N + (n < N ? n : 0)) * K;
@@ -463,12 +465,12 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const float *__restrict__ 
 // h bfloat16 [n, ldh]; ids / wts [n, top]; the experts' matrices stacked, bfloat16; scratch of the caller: rows int32 [n top],
 // tiles int32 [3 max_tiles + 1] (the last word: the number of tiles), act bfloat16 [n top, F], y float32 [n top, E];
 // out float32 [n, E].  E and F multiples of 8, ldh too.
-LGML_API int lgml_moe_experts_grouped(const void *h, int ldh, const int *ids, const float *wts, const void *wg, const void *wu, const void *wd,
+LGML_API int lgml_moe_experts_grouped(const void *h, int ldh, const int *ids, const float *wts, const void *wgu, const void *wd,
                                       int *rows, int *tiles, int max_tiles, void *act, float *y, float *out, int n_tokens, int E, int F, int X,
                                       int top, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && E > 0 && F > 0 && X > 0 && top > 0, "moe_experts_grouped: bad sizes");
     LGML_REQUIRE(E % 8 == 0 && F % 8 == 0 && ldh % 8 == 0, "moe_experts_grouped: widths %d, %d and the row stride %d must be multiples of 8", E, F, ldh);
-    LGML_REQUIRE((((uintptr_t)h | (uintptr_t)wg | (uintptr_t)wu | (uintptr_t)wd | (uintptr_t)act) & 15) == 0, "moe_experts_grouped: operands must be 16-byte aligned");
+    LGML_REQUIRE((((uintptr_t)h | (uintptr_t)wgu | (uintptr_t)wd | (uintptr_t)act) & 15) == 0, "moe_experts_grouped: operands must be 16-byte aligned");
     LGML_REQUIRE(X <= 8192, "moe_experts_grouped: at most 8192 experts");
     if (n_tokens == 0) return 0;
     const int n_rows = n_tokens * top;
@@ -481,12 +483,77 @@ LGML_API int lgml_moe_experts_grouped(const void *h, int ldh, const int *ids, co
     const size_t smem = (size_t)G_STAGES * G_STAGE_ELEMS * 2 + sizeof(int) * G_TM;
     if (need_smem(moe_tile_product_kernel<0>, smem, "moe_experts_grouped") || need_smem(moe_tile_product_kernel<1>, smem, "moe_experts_grouped")) return -1;
     lgml_launch(moe_tile_product_kernel<0>, g0, 256, smem, stream, (const __nv_bfloat16 *)h, ldh, (const int *)rows, (const int *)tiles,
-                (const int *)n_tiles, (const __nv_bfloat16 *)wg, (const __nv_bfloat16 *)wu, (const float *)nullptr, (__nv_bfloat16 *)act,
-                (float *)nullptr, E, F, top);
+                (const int *)n_tiles, (const __nv_bfloat16 *)wgu, (const float *)nullptr, (__nv_bfloat16 *)act, (float *)nullptr, E, F, top);
     lgml_launch(moe_tile_product_kernel<1>, g1, 256, smem, stream, (const __nv_bfloat16 *)act, F, (const int *)rows, (const int *)tiles,
-                (const int *)n_tiles, (const __nv_bfloat16 *)wd, (const __nv_bfloat16 *)nullptr, wts, (__nv_bfloat16 *)nullptr, y, F, E, top);
+                (const int *)n_tiles, (const __nv_bfloat16 *)wd, wts, (__nv_bfloat16 *)nullptr, y, F, E, top);
     const size_t total = (size_t)n_tokens * E;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     lgml_launch(moe_sum_kernel, blocks, 256, 0, stream, (const float *)y, out, n_tokens, E, top);
     return lgml_launch_status("moe_experts_grouped");
+}
+
+// ---------------------------------------------------------------------------------------------
+// The pieces around a grouped product that another library computes (the tcgen05 product with a tile list):
+//   moe_group_rows    the sorted rows and the tile list alone
+//   moe_gather_rows   the tokens' rows of h copied into tiles of 128 rows, tile t holding the rows the list gives it, and
+//                     where each (token, expert) row went
+//   moe_weighted_sum  out[t] = sum_s wts[t, s] y[pos[t top + s]], the chosen experts in their order
+// ---------------------------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(128) moe_gather_rows_kernel(const __nv_bfloat16 *__restrict__ h, int ldh, const int *__restrict__ rows,
+                                                              const int *__restrict__ tiles, int max_tiles, __nv_bfloat16 *__restrict__ a_perm,
+                                                              int *__restrict__ pos, int E, int top) {
+    pdl_trigger();
+    pdl_wait();
+    const int pr = blockIdx.x, tile = pr / G_TM, i = pr - tile * G_TM;
+    if (tile >= act_load(tiles + 3 * max_tiles) || i >= act_load(tiles + 3 * tile + 2)) return;
+    const int r = act_load(rows + act_load(tiles + 3 * tile + 1) + i);
+    if (threadIdx.x == 0) pos[r] = pr;
+    const uint4 *src = reinterpret_cast<const uint4 *>(h + (size_t)(r / top) * ldh);
+    uint4 *dst = reinterpret_cast<uint4 *>(a_perm + (size_t)pr * E);
+    for (int c = threadIdx.x; c < E / 8; c += blockDim.x) dst[c] = act_load(src + c);
+}
+
+__global__ void __launch_bounds__(256) moe_weighted_sum_kernel(const float *__restrict__ y, const int *__restrict__ pos, const float *__restrict__ wts,
+                                                               float *__restrict__ out, int n_tokens, int E, int top) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t total = (size_t)n_tokens * E;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / E, j = i - t * E;
+        float s = 0.f;
+        for (int k = 0; k < top; ++k) s = fmaf(act_load(wts + t * top + k), act_load(y + (size_t)act_load(pos + t * top + k) * E + j), s);
+        out[i] = s;
+    }
+}
+}  // namespace
+
+// rows int32 [n top]; tiles int32 [3 max_tiles + 1] (the last word: the number of tiles)
+LGML_API int lgml_moe_group_rows(const int *ids, int *rows, int *tiles, int max_tiles, int n_tokens, int X, int top, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && X > 0 && X <= 8192 && top > 0, "moe_group_rows: bad sizes");
+    const int n_rows = n_tokens * top;
+    const int need = (n_rows + G_TM - 1) / G_TM + (X < n_rows ? X : n_rows);
+    LGML_REQUIRE(max_tiles >= need, "moe_group_rows: room for %d tiles, %d may be needed", max_tiles, need);
+    if (n_tokens == 0) return 0;
+    lgml_launch(moe_group_kernel, 1, 1024, sizeof(int) * 4 * (size_t)X, stream, ids, n_rows, X, rows, tiles, tiles + 3 * max_tiles, max_tiles);
+    return lgml_launch_status("moe_group_rows");
+}
+
+// a_perm bfloat16 [max_tiles 128, E]; pos int32 [n top]
+LGML_API int lgml_moe_gather_rows(const void *h, int ldh, const int *rows, const int *tiles, int max_tiles, void *a_perm, int *pos, int E, int top,
+                                  cudaStream_t stream) {
+    LGML_REQUIRE(max_tiles > 0 && E > 0 && E % 8 == 0 && ldh % 8 == 0 && top > 0, "moe_gather_rows: bad sizes");
+    LGML_REQUIRE((((uintptr_t)h | (uintptr_t)a_perm) & 15) == 0, "moe_gather_rows: operands must be 16-byte aligned");
+    lgml_launch(moe_gather_rows_kernel, max_tiles * G_TM, 128, 0, stream, (const __nv_bfloat16 *)h, ldh, rows, tiles, max_tiles, (__nv_bfloat16 *)a_perm, pos,
+                E, top);
+    return lgml_launch_status("moe_gather_rows");
+}
+
+LGML_API int lgml_moe_weighted_sum(const float *y, const int *pos, const float *wts, float *out, int n_tokens, int E, int top, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && E > 0 && top > 0, "moe_weighted_sum: bad sizes");
+    if (n_tokens == 0) return 0;
+    const size_t total = (size_t)n_tokens * E;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    lgml_launch(moe_weighted_sum_kernel, blocks, 256, 0, stream, y, pos, wts, out, n_tokens, E, top);
+    return lgml_launch_status("moe_weighted_sum");
 }

@@ -27,7 +27,7 @@ _STATUS_TEXT = {
 
 AHEAD_BYTES = 24 << 20      # weights asked of L2 ahead, per layer (measured best at 24 to 32 MiB)
 AHEAD_MAX_BATCH = 4         # ... in captured steps of at most this many requests (at 8 the step gets slower)
-MOE_GROUPED_ROWS = 32       # (token, expert) rows of a step from which the experts run as grouped tiles
+MOE_GROUPED_ROWS = 8        # (token, expert) rows of a step from which the experts run as grouped tiles
 MAX_RESULT = 4096     # most sampled rows of a step whose ids travel with the status word
 
 
@@ -140,12 +140,15 @@ class Runtime:
                                   window, self.status, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first)
 
     # ---- mixture of experts ------------------------------------------------------------
-    def moe_experts(self, h, ids, wts, w_gate, w_up, w_down) -> torch.Tensor:
+    def moe_experts(self, h, ids, wts, w_gu, w_down) -> torch.Tensor:
         """The chosen experts' weighted outputs, float32 [tokens, width]: a block per (token, expert) for few
-        tokens and on the 32-bit path, tiles of one expert's rows on tensor cores for many."""
-        if ids.numel() >= MOE_GROUPED_ROWS and ops.moe_grouped_supports(h, w_gate):
-            return ops.moe_experts_grouped(h, ids, wts, w_gate, w_up, w_down)
-        return ops.moe_experts_rows(h, ids, wts, w_gate, w_up, w_down)
+        tokens and on the 32-bit path; for many, tiles of one expert's rows as grouped products on tcgen05
+        (``LGML_MOE_GROUPED=mma``: the same tiles on ``mma.sync``)."""
+        if ids.numel() >= MOE_GROUPED_ROWS and ops.moe_grouped_supports(h, w_gu):
+            if os.environ.get("LGML_MOE_GROUPED") == "mma":
+                return ops.moe_experts_grouped(h, ids, wts, w_gu, w_down)
+            return ops.moe_experts_tcgen05(h, ids, wts, w_gu, w_down, self.status)
+        return ops.moe_experts_rows(h, ids, wts, w_gu, w_down)
 
     # ---- faults ------------------------------------------------------------------------
     def check_status(self, code: Optional[int] = None) -> None:

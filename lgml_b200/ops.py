@@ -836,29 +836,35 @@ def moe_router(h: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch
     return ids, wts
 
 
-def moe_experts_rows(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
-    """out[t] = sum_s wts[t, s] W_down[e] (silu(W_gate[e] h_t) * (W_up[e] h_t)), e = ids[t, s]: float32
-    [tokens, E].  The experts' matrices stacked: gate and up [X, F, E], down [X, E, F].  A block per
-    (token, chosen expert): the form for few tokens and for the 32-bit path."""
-    _need(h, "experts' input", ndim=2)
-    for t, what in ((w_gate, "gate"), (w_up, "up"), (w_down, "down")):
+def _moe_shapes(h, ids, wts, w_gu, w_down, who: str):
+    for t, what in ((w_gu, "gate|up"), (w_down, "down")):
         _need(t, f"experts' {what} matrices", h.dtype, 3)
         if not t.is_contiguous():
-            raise KernelError(f"moe_experts_rows: the {what} matrices must be contiguous")
+            raise KernelError(f"{who}: the {what} matrices must be contiguous")
     _need(ids, "chosen experts", torch.int32, 2)
     _need(wts, "experts' weights", torch.float32, 2)
-    ldh = _rows_contiguous(h, "experts' input")
     n, E = h.shape
-    X, F, _ = w_gate.shape
-    top = ids.shape[1]
-    if tuple(w_gate.shape) != (X, F, E) or tuple(w_up.shape) != (X, F, E) or tuple(w_down.shape) != (X, E, F) or tuple(ids.shape) != (n, top) \
+    X, F2, _ = w_gu.shape
+    F, top = F2 // 2, ids.shape[1]
+    if tuple(w_gu.shape) != (X, 2 * F, E) or tuple(w_down.shape) != (X, E, F) or tuple(ids.shape) != (n, top) \
             or tuple(wts.shape) != (n, top) or not ids.is_contiguous() or not wts.is_contiguous():
-        raise KernelError(f"moe_experts_rows: shapes disagree: h {tuple(h.shape)}, gate {tuple(w_gate.shape)}, down {tuple(w_down.shape)}, ids {tuple(ids.shape)}")
+        raise KernelError(f"{who}: shapes disagree: h {tuple(h.shape)}, gate|up {tuple(w_gu.shape)}, down {tuple(w_down.shape)}, ids {tuple(ids.shape)}")
+    return n, E, F, X, top
+
+
+def moe_experts_rows(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_s wts[t, s] W_down[e] (silu(W_gate[e] h_t) * (W_up[e] h_t)), e = ids[t, s]: float32
+    [tokens, E].  The experts' matrices stacked: ``w_gu`` [X, 2 F, E] with the gate row of a feature followed
+    by its up row, ``w_down`` [X, E, F].  A block per (token, chosen expert): the form for few tokens and for
+    the 32-bit path."""
+    _need(h, "experts' input", ndim=2)
+    ldh = _rows_contiguous(h, "experts' input")
+    n, E, F, X, top = _moe_shapes(h, ids, wts, w_gu, w_down, "moe_experts_rows")
     act = torch.empty((n * top, F), dtype=h.dtype, device=h.device)
     out = torch.empty((n, E), dtype=torch.float32, device=h.device)
-    fn = _fn("moe", "lgml_moe_experts_rows", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+    fn = _fn("moe", "lgml_moe_experts_rows", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                               c_int, c_int, c_int, c_void_p])
-    _check("moe", fn(_ptr(h), dtype_code(h.dtype), ldh, _ptr(ids), _ptr(wts), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _ptr(act), _ptr(out), n, E, F, X,
+    _check("moe", fn(_ptr(h), dtype_code(h.dtype), ldh, _ptr(ids), _ptr(wts), _ptr(w_gu), _ptr(w_down), _ptr(act), _ptr(out), n, E, F, X,
                      top, _stream()), "moe_experts_rows")
     return out
 
@@ -866,43 +872,75 @@ def moe_experts_rows(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_ga
 MOE_TILE_ROWS = 128
 
 
-def moe_grouped_supports(h: torch.Tensor, w_gate: torch.Tensor) -> bool:
-    """Whether ``moe_experts_grouped`` takes these operands: bfloat16, widths that are multiples of 8."""
+def moe_grouped_supports(h: torch.Tensor, w_gu: torch.Tensor) -> bool:
+    """Whether the grouped forms take these operands: bfloat16, widths that are multiples of 8."""
     return (h.dtype == torch.bfloat16 and h.dim() == 2 and h.stride(1) == 1 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
-            and w_gate.shape[1] % 8 == 0 and w_gate.shape[2] % 8 == 0)
+            and w_gu.shape[1] % 16 == 0 and w_gu.shape[2] % 8 == 0)
 
 
-def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
-    """``moe_experts_rows`` for many tokens, bfloat16: the (token, chosen expert) rows sorted by expert on
-    the device and cut into tiles of 128 rows of one expert, each tile a product on tensor cores; float32
-    [tokens, E].  No host value is read: the launches are the same whatever the router chose."""
+def _moe_tiles(n_rows: int, X: int) -> int:
+    return -(-n_rows // MOE_TILE_ROWS) + min(X, n_rows)
+
+
+def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """``moe_experts_rows`` for many tokens, bfloat16, on ``mma.sync``: the (token, chosen expert) rows sorted by
+    expert on the device and cut into tiles of 128 rows of one expert; float32 [tokens, E].  No host value is
+    read: the launches are the same whatever the router chose.  (The form ``moe_experts_tcgen05`` replaced;
+    ``LGML_MOE_GROUPED=mma`` selects it.)"""
     _need(h, "experts' input", torch.bfloat16, 2)
-    for t, what in ((w_gate, "gate"), (w_up, "up"), (w_down, "down")):
-        _need(t, f"experts' {what} matrices", torch.bfloat16, 3)
-        if not t.is_contiguous():
-            raise KernelError(f"moe_experts_grouped: the {what} matrices must be contiguous")
-    _need(ids, "chosen experts", torch.int32, 2)
-    _need(wts, "experts' weights", torch.float32, 2)
     ldh = _rows_contiguous(h, "experts' input")
-    n, E = h.shape
-    X, F, _ = w_gate.shape
-    top = ids.shape[1]
-    if tuple(w_gate.shape) != (X, F, E) or tuple(w_up.shape) != (X, F, E) or tuple(w_down.shape) != (X, E, F) or tuple(ids.shape) != (n, top) \
-            or tuple(wts.shape) != (n, top) or not ids.is_contiguous() or not wts.is_contiguous():
-        raise KernelError(f"moe_experts_grouped: shapes disagree: h {tuple(h.shape)}, gate {tuple(w_gate.shape)}, down {tuple(w_down.shape)}, ids {tuple(ids.shape)}")
-    if not moe_grouped_supports(h, w_gate):
+    n, E, F, X, top = _moe_shapes(h, ids, wts, w_gu, w_down, "moe_experts_grouped")
+    if not moe_grouped_supports(h, w_gu):
         raise KernelError("moe_experts_grouped: widths and row strides must be multiples of 8 and the input 16-byte aligned")
     n_rows = n * top
-    max_tiles = -(-n_rows // MOE_TILE_ROWS) + min(X, n_rows)
+    max_tiles = _moe_tiles(n_rows, X)
     rows = torch.empty(n_rows, dtype=torch.int32, device=h.device)
     tiles = torch.empty(3 * max_tiles + 1, dtype=torch.int32, device=h.device)
     act = torch.empty((n_rows, F), dtype=torch.bfloat16, device=h.device)
     y = torch.empty((n_rows, E), dtype=torch.float32, device=h.device)
     out = torch.empty((n, E), dtype=torch.float32, device=h.device)
-    fn = _fn("moe", "lgml_moe_experts_grouped", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+    fn = _fn("moe", "lgml_moe_experts_grouped", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check("moe", fn(_ptr(h), ldh, _ptr(ids), _ptr(wts), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _ptr(rows), _ptr(tiles), max_tiles, _ptr(act),
+    _check("moe", fn(_ptr(h), ldh, _ptr(ids), _ptr(wts), _ptr(w_gu), _ptr(w_down), _ptr(rows), _ptr(tiles), max_tiles, _ptr(act),
                      _ptr(y), _ptr(out), n, E, F, X, top, _stream()), "moe_experts_grouped")
+    return out
+
+
+def moe_experts_tcgen05(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor,
+                        status: torch.Tensor) -> torch.Tensor:
+    """``moe_experts_rows`` for many tokens, bfloat16, on tcgen05: the (token, chosen expert) rows are sorted by
+    expert on the device, the tokens' rows gathered into tiles of 128 rows of one expert, and the two products
+    run as grouped products of the tcgen05 kernel (a tile reads the matrices of its expert; the gate|up product
+    applies the SiLU gate in its epilogue); a token's rows are then added, weighted, in the order of its experts.
+    float32 [tokens, E].  No host value is read."""
+    _need(h, "experts' input", torch.bfloat16, 2)
+    ldh = _rows_contiguous(h, "experts' input")
+    n, E, F, X, top = _moe_shapes(h, ids, wts, w_gu, w_down, "moe_experts_tcgen05")
+    if not moe_grouped_supports(h, w_gu):
+        raise KernelError("moe_experts_tcgen05: widths and row strides must be multiples of 8 and the input 16-byte aligned")
+    n_rows = n * top
+    max_tiles = _moe_tiles(n_rows, X)
+    dev = h.device
+    rows = torch.empty(n_rows, dtype=torch.int32, device=dev)
+    pos = torch.empty(n_rows, dtype=torch.int32, device=dev)
+    tiles = torch.empty(3 * max_tiles + 1, dtype=torch.int32, device=dev)
+    a_perm = torch.empty((max_tiles * MOE_TILE_ROWS, E), dtype=torch.bfloat16, device=dev)
+    act = torch.empty((max_tiles * MOE_TILE_ROWS, F), dtype=torch.bfloat16, device=dev)
+    y = torch.empty((max_tiles * MOE_TILE_ROWS, E), dtype=torch.float32, device=dev)
+    out = torch.empty((n, E), dtype=torch.float32, device=dev)
+    stream = _stream()
+    fn = _fn("moe", "lgml_moe_group_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check("moe", fn(_ptr(ids), _ptr(rows), _ptr(tiles), max_tiles, n, X, top, stream), "moe_group_rows")
+    fn = _fn("moe", "lgml_moe_gather_rows", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check("moe", fn(_ptr(h), ldh, _ptr(rows), _ptr(tiles), max_tiles, _ptr(a_perm), _ptr(pos), E, top, stream), "moe_gather_rows")
+    fn = _fn("gemm_tcgen05", "lgml_gemm_tcgen05_grouped", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                                           c_void_p, c_void_p])
+    _check("gemm_tcgen05", fn(_ptr(a_perm), _ptr(w_gu), _ptr(act), 0, max_tiles, 2 * F, E, X, F, _ptr(tiles), 1, _ptr(status), stream),
+           "gemm_tcgen05_grouped")
+    _check("gemm_tcgen05", fn(_ptr(act), _ptr(w_down), _ptr(y), 1, max_tiles, E, F, X, E, _ptr(tiles), 0, _ptr(status), stream),
+           "gemm_tcgen05_grouped")
+    fn = _fn("moe", "lgml_moe_weighted_sum", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check("moe", fn(_ptr(y), _ptr(pos), _ptr(wts), _ptr(out), n, E, top, stream), "moe_weighted_sum")
     return out
 
 

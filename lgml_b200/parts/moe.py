@@ -5,8 +5,8 @@
     y      = sum_e w_e W_down,e (act(W_gate,e h) * (W_up,e h)),   act = silu
 
 Tensors: ``.router`` [X, E], ``.router.b`` [X], ``.e<i>.gate`` / ``.up`` [F, E], ``.e<i>.down`` [E, F]
-(no biases in the experts).  The experts' matrices are stacked when they are bound, so that a kernel
-finds expert e at a fixed stride.
+(no biases in the experts).  The experts' matrices are stacked when they are bound (gate and up of a
+feature as neighbouring rows), so that a kernel finds expert e at a fixed stride.
 """
 from __future__ import annotations
 
@@ -25,7 +25,7 @@ class RoutedExperts(Part):
             raise ValueError(f"{top} of {n_experts} experts cannot be chosen")
         self.width, self.inner, self.n_experts, self.top = width, inner, n_experts, top
         self.router_bias = bool(router_bias)
-        self.w_router = self.b_router = self.wg = self.wu = self.wd = None
+        self.w_router = self.b_router = self.w_gu = self.wd = None
 
     def tensor_specs(self, prefix):
         E, F = self.width, self.inner
@@ -40,15 +40,18 @@ class RoutedExperts(Part):
     def bind(self, prefix, tensors, rt):
         self.w_router = tensors[prefix + ".router"].contiguous()
         self.b_router = tensors[prefix + ".router.b"] if self.router_bias else None
-        stack = lambda name: torch.stack([tensors[f"{prefix}.e{e}.{name}"] for e in range(self.n_experts)], dim=0).contiguous()
-        self.wg, self.wu, self.wd = stack("gate"), stack("up"), stack("down")
+        # gate and up of an expert as one matrix [2 F, E], the gate row of a feature followed by its up row: a product's
+        # epilogue, and a warp of the row form, then has both of a feature
+        pairs = lambda e: torch.stack([tensors[f"{prefix}.e{e}.gate"], tensors[f"{prefix}.e{e}.up"]], dim=1).reshape(2 * self.inner, self.width)
+        self.w_gu = torch.stack([pairs(e) for e in range(self.n_experts)], dim=0).contiguous()
+        self.wd = torch.stack([tensors[f"{prefix}.e{e}.down"] for e in range(self.n_experts)], dim=0).contiguous()
         for e in range(self.n_experts):      # the stacked copies are what runs
             for name in ("gate", "up", "down"):
                 tensors.pop(f"{prefix}.e{e}.{name}", None)
 
     def forward(self, rt, h):
         ids, wts = ops.moe_router(h, self.w_router, self.b_router, self.top)
-        return rt.moe_experts(h, ids, wts, self.wg, self.wu, self.wd)
+        return rt.moe_experts(h, ids, wts, self.w_gu, self.wd)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

@@ -292,7 +292,7 @@ def test_clamped_gate_in_the_products_epilogue(M):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("X,top,E,F", [(5, 2, 64, 24), (1, 1, 36, 20), (4, 4, 40, 12), (12, 3, 96, 40), (40, 6, 128, 64)])
+@pytest.mark.parametrize("X,top,E,F", [(5, 2, 64, 24), (1, 1, 36, 20), (4, 4, 40, 12), (12, 3, 96, 40), (40, 6, 128, 64), (3, 2, 256, 520)])
 def test_router_and_experts(dtype, X, top, E, F):
     """The chosen experts are those of the plain router (logits kept apart), ties go to the lower index, and
     the weighted sum of the experts' outputs is the plain one; 300 tokens, so that the grouped form runs too."""
@@ -312,13 +312,18 @@ def test_router_and_experts(dtype, X, top, E, F):
     ids, wts = ops.moe_router(hd, W["f.router"].float().to(DEV), W["f.router.b"].float().to(DEV), top)
     z = h @ W["f.router"].T + W["f.router.b"]
     assert torch.equal(ids.cpu().long(), torch.argsort(-z, dim=1, stable=True)[:, :top])
-    stack = lambda n: torch.stack([W[f"f.e{e}.{n}"] for e in range(X)]).to(dtype).to(DEV)
+    w_gu = torch.stack([torch.stack([W[f"f.e{e}.gate"], W[f"f.e{e}.up"]], dim=1).reshape(2 * F, E) for e in range(X)]).to(dtype).to(DEV)
+    w_down = torch.stack([W[f"f.e{e}.down"] for e in range(X)]).to(dtype).to(DEV)
     tol = (3e-5 if dtype == torch.float32 else 2e-2) * (1.0 + float(want.abs().max()))
-    out = ops.moe_experts_rows(hd, ids, wts, stack("gate"), stack("up"), stack("down"))
+    out = ops.moe_experts_rows(hd, ids, wts, w_gu, w_down)
     assert float((out.double().cpu() - want).abs().max()) < tol
-    if dtype == torch.bfloat16 and ops.moe_grouped_supports(hd, stack("gate")):
-        out2 = ops.moe_experts_grouped(hd, ids, wts, stack("gate"), stack("up"), stack("down"))
+    if dtype == torch.bfloat16 and ops.moe_grouped_supports(hd, w_gu):
+        out2 = ops.moe_experts_grouped(hd, ids, wts, w_gu, w_down)
         assert float((out2.double().cpu() - want).abs().max()) < tol
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        out3 = ops.moe_experts_tcgen05(hd, ids, wts, w_gu, w_down, status)
+        assert int(status.item()) == 0
+        assert float((out3.double().cpu() - want).abs().max()) < tol
     # ties: equal logits go to the lower index
     ids2, wts2 = ops.moe_router(torch.zeros(3, E, dtype=dtype, device=DEV), W["f.router"].float().to(DEV), None, top)
     assert torch.equal(ids2.cpu(), torch.arange(top, dtype=torch.int32).expand(3, top))
