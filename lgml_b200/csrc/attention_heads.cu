@@ -6,7 +6,7 @@
 //                    latent c; its last Dr columns are a rotated key part shared by all heads;
 //                    both go into one cell of the cache [c | k_rot].  The queries' rotated part is
 //                    rotated and placed behind the R columns that head_linear fills
-//   head_linear      a product per head: out[t, h, :] = W[h] x[t, h, :], for the up-projections of
+//   head_linear      a product per head (FMA units; tensor cores from 32 tokens on): out[t, h, :] = W[h] x[t, h, :], for the up-projections of
 //                    latent attention taken to the query side (q W_uk) and to the output side
 //                    (W_uv o), so that attention itself runs on the cached latent
 //
@@ -171,6 +171,72 @@ __global__ void __launch_bounds__(256) head_linear_kernel(const T *__restrict__ 
             if (t < n && o < O) out[(size_t)t * ldo + (size_t)h * oh + o] = from_f32<T>(acc[i][j]);
         }
 }
+
+// The same product on tensor cores (mma.sync m16n8k16, float32 accumulation) for many tokens, bfloat16: a block of four
+// warps takes 64 tokens x 64 outputs of one head, K in steps of 64 through shared memory (16-byte cp.async, zeros past
+// the edges); a warp owns 16 tokens.  A row's sums do not depend on which tile it lies in.
+constexpr int HM_T = 64, HM_K = 64, HM_LD = HM_K + 8;
+__device__ __forceinline__ uint32_t hm_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__global__ void __launch_bounds__(128) head_linear_mma_kernel(const __nv_bfloat16 *__restrict__ x, int ldx, int xh, const __nv_bfloat16 *__restrict__ w,
+                                                              __nv_bfloat16 *__restrict__ out, int ldo, int oh, int n, int O, int K) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ __align__(16) __nv_bfloat16 As[HM_T * HM_LD];
+    __shared__ __align__(16) __nv_bfloat16 Bs[HM_T * HM_LD];
+    const int h = blockIdx.z, t0 = blockIdx.x * HM_T, o0 = blockIdx.y * HM_T;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int mat = lane >> 3, mrow = lane & 7;
+    const __nv_bfloat16 *wh = w + (size_t)h * O * K;
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += HM_K) {
+        for (int c = threadIdx.x; c < HM_T * (HM_K / 8); c += 128) {
+            const int r = c / (HM_K / 8), col = (c - r * (HM_K / 8)) * 8;
+            const bool oka = t0 + r < n && k0 + col < K, okb = o0 + r < O && k0 + col < K;
+            const __nv_bfloat16 *sa = x + (size_t)(oka ? t0 + r : 0) * ldx + (size_t)h * xh + (oka ? k0 + col : 0);
+            const __nv_bfloat16 *sb = wh + (size_t)(okb ? o0 + r : 0) * K + (okb ? k0 + col : 0);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(hm_smem(As + r * HM_LD + col)), "l"(sa), "r"(oka ? 16 : 0) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(hm_smem(Bs + r * HM_LD + col)), "l"(sb), "r"(okb ? 16 : 0) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < HM_K / 16; ++ks) {
+            uint32_t a[4];
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                         : "r"(hm_smem(As + (warp * 16 + (mat & 1) * 8 + mrow) * HM_LD + ks * 16 + (mat >> 1) * 8)));
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b[4];
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3])
+                             : "r"(hm_smem(Bs + (np * 16 + (mat >> 1) * 8 + mrow) * HM_LD + ks * 16 + (mat & 1) * 8)));
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                             : "+f"(acc[2 * np][0]), "+f"(acc[2 * np][1]), "+f"(acc[2 * np][2]), "+f"(acc[2 * np][3])
+                             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+                asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                             : "+f"(acc[2 * np + 1][0]), "+f"(acc[2 * np + 1][1]), "+f"(acc[2 * np + 1][2]), "+f"(acc[2 * np + 1][3])
+                             : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[2]), "r"(b[3]));
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int t = t0 + warp * 16 + (lane >> 2) + rr * 8;
+        if (t >= n) continue;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int o = o0 + nt * 8 + (lane & 3) * 2 + i;
+                if (o < O) out[(size_t)t * ldo + (size_t)h * oh + o] = __float2bfloat16_rn(acc[nt][rr * 2 + i]);
+            }
+    }
+}
 }  // namespace
 
 LGML_API int lgml_diff_combine(const void *in, int in_dtype, int ldi, void *out, int out_dtype, int ldo, int n_tokens, int H, int G, int Dv,
@@ -218,6 +284,12 @@ LGML_API int lgml_head_linear(const void *x, int ldx, int xh, const void *w, voi
     LGML_REQUIRE(n_tokens >= 0 && H > 0 && O > 0 && K > 0, "head_linear: bad sizes");
     LGML_REQUIRE(H <= 65535 && (O + HL_TN - 1) / HL_TN <= 65535, "head_linear: too many heads or outputs");
     if (n_tokens == 0) return 0;
+    if (dtype == LGML_BF16 && n_tokens >= 32 && K % 8 == 0 && ldx % 8 == 0 && xh % 8 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
+        dim3 gm((n_tokens + HM_T - 1) / HM_T, (O + HM_T - 1) / HM_T, H);
+        lgml_launch(head_linear_mma_kernel, gm, 128, 0, stream, (const __nv_bfloat16 *)x, ldx, xh, (const __nv_bfloat16 *)w, (__nv_bfloat16 *)out, ldo, oh,
+                    n_tokens, O, K);
+        return lgml_launch_status("head_linear");
+    }
     dim3 grid((n_tokens + HL_TM - 1) / HL_TM, (O + HL_TN - 1) / HL_TN, H);
     if (dtype == LGML_F32)
         lgml_launch(head_linear_kernel<float>, grid, 256, 0, stream, (const float *)x, ldx, xh, (const float *)w, (float *)out, ldo, oh, n_tokens, O, K);

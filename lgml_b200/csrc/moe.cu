@@ -518,6 +518,21 @@ __global__ void __launch_bounds__(256) moe_weighted_sum_kernel(const float *__re
                                                                float *__restrict__ out, int n_tokens, int E, int top) {
     pdl_trigger();
     pdl_wait();
+    if (E % 4 == 0 && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        const int quads = E / 4;
+        const size_t total = (size_t)n_tokens * quads;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+            const size_t t = i / quads, j = (i - t * quads) * 4;
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < top; ++k) {
+                const float w = act_load(wts + t * top + k);
+                const float4 v = act_load(reinterpret_cast<const float4 *>(y + (size_t)act_load(pos + t * top + k) * E + j));
+                s.x = fmaf(w, v.x, s.x), s.y = fmaf(w, v.y, s.y), s.z = fmaf(w, v.z, s.z), s.w = fmaf(w, v.w, s.w);
+            }
+            *reinterpret_cast<float4 *>(out + t * E + j) = s;
+        }
+        return;
+    }
     const size_t total = (size_t)n_tokens * E;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / E, j = i - t * E;
