@@ -16,6 +16,7 @@ pos * base^(-2i / rope_dims).
 """
 from __future__ import annotations
 
+import dataclasses
 from typing import Optional
 
 import torch
@@ -72,10 +73,19 @@ class LatentAttention(Part):
         q_plain, q_full = ops.latent_prepare(proj[:, :nq], proj[:, nq:], self.norm_w, self.eps, self.inv_freq, self.rope_dims, batch.positions,
                                              batch.seq_of_token, cache.block_table, cache.k, H, D, Dr, R, rt.status, write_kv=cache.writable)
         ops.head_linear(q_plain, self.w_uk_t, q_full, D, R + Dr)
-        mix = torch.empty((n, H * R), dtype=h.dtype, device=h.device)          # sum_j w_j c_j per head
-        rt.sink_attention(q_full, batch, cache, mix, H, self.scale, 0, None, None, None)
         o = torch.empty((n, H * Dv), dtype=h.dtype, device=h.device)
-        ops.head_linear(mix, self.w_uv, o, R, Dv)
+        if rt.dtype == torch.bfloat16 and (R + Dr) in (64, 128):
+            # A cell of 64 or 128 numbers is a head size the plain causal attention kernels are built for (tcgen05 for
+            # prompts, the split form for decoding): the whole cell serves as the value, and the product behind
+            # attention reads only the first R entries of every head's result.
+            whole = dataclasses.replace(cache, v=cache.k, writable=False)
+            mix = torch.empty((n, H * (R + Dr)), dtype=h.dtype, device=h.device)
+            rt.attention(q_full, batch, whole, mix, H, self.scale, 0)
+            ops.head_linear(mix, self.w_uv, o, R + Dr, Dv)
+        else:
+            mix = torch.empty((n, H * R), dtype=h.dtype, device=h.device)          # sum_j w_j c_j per head
+            rt.sink_attention(q_full, batch, cache, mix, H, self.scale, 0, None, None, None)
+            ops.head_linear(mix, self.w_uv, o, R, Dv)
         return rt.linear(o, self.wo, partials_ok=True)
 
 
