@@ -363,8 +363,14 @@ __global__ void __launch_bounds__(256) dyt_norm_kernel(const Args a, const float
         if (a.delta) add_delta<TD>(a, xr, reinterpret_cast<const TD *>(a.delta) + src * width, i, width, v);
         load_quad_const(a.weight, i, width, a.vec, w);
         load_quad_const(shift, i, width, a.vec, b);
+        // a bfloat16 result takes tanh as 1 - 2 / (e^(2x) + 1) from the fast exponential and division (an error of a few
+        // 1e-7, far below that rounding); a float32 result takes the library's
 #pragma unroll
-        for (int q = 0; q < PER; ++q) y[q] = fmaf(tanhf(al * v[q]), w[q], b[q]);
+        for (int q = 0; q < PER; ++q) {
+            const float z = al * v[q];
+            const float th = sizeof(TO) == 2 ? 1.0f - __fdividef(2.0f, __expf(2.0f * z) + 1.0f) : tanhf(z);
+            y[q] = fmaf(th, w[q], b[q]);
+        }
         store_quad(reinterpret_cast<TO *>(a.out) + (size_t)r * width, i, width, a.vec, y);
     }
 }
@@ -487,7 +493,7 @@ template <typename TD>
 static int dyt_dispatch(rms::Args &a, const TD *, const float *shift, const float *alpha, float pre, int out_dtype, int n_rows, cudaStream_t stream) {
     const size_t total = (size_t)n_rows * ((a.width + 3) / 4);
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 64 ? (total + threads - 1) / threads : 148 * 64);
     if (out_dtype == LGML_F32) lgml_launch(rms::dyt_norm_kernel<TD, float>, blocks, threads, 0, stream, a, shift, alpha, pre, n_rows);
     else lgml_launch(rms::dyt_norm_kernel<TD, __nv_bfloat16>, blocks, threads, 0, stream, a, shift, alpha, pre, n_rows);
     return lgml_launch_status("dyt_norm");

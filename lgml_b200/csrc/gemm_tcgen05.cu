@@ -1097,7 +1097,7 @@ LGML_API int lgml_gemm_tcgen05_glu_clamped(const void *x, const void *w, void *y
 // group[3 t] * N ... + N - 1 of w [n_groups * N, K] (the matrices of n_groups experts stacked); group[3 max_tiles] is the
 // number of tiles in use, read on the device (the list is written by the kernel ahead).  y [max_tiles * 128, N], or
 // [.., N / 2] with swiglu = 1 (rows of w in (gate, up) pairs, y = silu(gate) * up).  The single-CTA persistent kernel with
-// 128 x 256 tiles; rows of a tile past an expert's last feature are computed from the next expert's rows and not stored.
+// 128 x 256 tiles (128 x 128 where those would be fewer than the SMs); rows of a tile past an expert's last feature are computed from the next expert's rows and not stored.
 LGML_API int lgml_gemm_tcgen05_grouped(const void *x, const void *w, void *y, int y_f32, int max_tiles, int N, int K, int n_groups, int ldy,
                                        const int *group, int swiglu, int *status, cudaStream_t stream) {
     LGML_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && n_groups > 0 && group != nullptr, "gemm_tcgen05_grouped: bad sizes");
@@ -1120,14 +1120,17 @@ LGML_API int lgml_gemm_tcgen05_grouped(const void *x, const void *w, void *y, in
     p.transposed = 0;
     p.rows_a = max_tiles * BM;
     p.rows_b = N;
+    // few tiles (a decode step's handful of rows per expert): columns in blocks of 128, so that more CTAs stream the weights
+    const int bn = max_tiles * ((N + 255) / 256) < 148 ? 128 : 256;
     p.tiles_a = max_tiles;
-    p.tiles_b = (N + 255) / 256;
+    p.tiles_b = (N + bn - 1) / bn;
     p.group = group, p.group_max_tiles = max_tiles, p.group_rows_b = N;
     CUtensorMap ma, mb;
     int rc;
     if ((rc = make_map(&ma, x, (long long)max_tiles * BM, K, K, BM))) return rc;
-    if ((rc = make_map(&mb, w, (long long)n_groups * N, K, K, 256))) return rc;
+    if ((rc = make_map(&mb, w, (long long)n_groups * N, K, K, bn))) return rc;
     const int n_tiles = p.tiles_a * p.tiles_b;
     dim3 grid(n_tiles < 148 ? n_tiles : 148, 1, 1);
+    if (bn == 128) return launch<128, 6, 1>(ma, mb, p, grid, stream);
     return launch<256, 4, 2>(ma, mb, p, grid, stream);
 }

@@ -494,15 +494,24 @@ def test_greedy_generation_through_the_engine(model, dtype):
         assert solo == outs[0]
 
 
-def test_trace_run_as_a_process(model, tmp_path):
+@pytest.mark.parametrize("variant", ["float32", "bfloat16-switches"])
+def test_trace_run_as_a_process(model, tmp_path, variant):
+    """bin/trace_run as a process on a mixed trace; in bfloat16 with the older of each pair of implementations switched on
+    (the experts' tiles on mma.sync, the clamped gate as a kernel of its own)."""
+    import os
+
     name, cfg, made = model
-    weights, folder = made["float32"]
-    seqs = sequences(cfg, [70, 20, 131], seed=300)
+    dtype = variant.split("-")[0]
+    weights, folder = made[dtype]
+    seqs = sequences(cfg, [70, 20, 131], seed=300, weights=weights if dtype == "bfloat16" else None)
     trace = H.trace_mixed(seqs, max_tokens=64 * 4, seed=2, max_live=2)
     out = tmp_path / "out"
-    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(out),
+    env = dict(os.environ)
+    if variant.endswith("switches"):
+        env.update(LGML_MOE_GROUPED="mma", LGML_GLU_FUSED="0")
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
                            "--max-tokens", str(64 * 4)], input="\n".join(json.dumps(s) for s in trace) + "\n", text=True,
-                          capture_output=True, timeout=600)
+                          capture_output=True, timeout=600, env=env)
     assert proc.returncode == 0, proc.stderr[-2000:]
     done = [ln for ln in proc.stdout.splitlines() if ln.startswith("done ")]
     assert done == [f"done {s['step']}" for s in trace]
@@ -516,7 +525,7 @@ def test_trace_run_as_a_process(model, tmp_path):
                 r += 1
             fed[e["id"]] += len(e["tokens"])
         assert r == rows.shape[0]
-    L.compare(got, cfg, weights, seqs, **TOL["float32"])
+    L.compare(got, cfg, weights, seqs, **TOL[dtype])
 
 
 def test_command_line_generates_with_the_folders_architecture(model):
