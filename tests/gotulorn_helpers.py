@@ -73,7 +73,7 @@ NO_WINDOW = config(83, 48, [
 # layers run on them.
 WIDE_HEADS = config(101, 96, [
     attention(4, 2, 64, 64, scale=0.12, diff=0.3, window=100, keep_first=6, mlp=dense(72, 2.0)),
-    latent(4, 32, 32, 32, 96, scale=0.1, base=20000.0, mlp=moe(40, 8, 2)),
+    latent(4, 32, 32, 32, 96, scale=0.1, base=30000.0, mlp=moe(40, 8, 2)),
     attention(4, 2, 64, 64, scale=0.12, diff=0.2, window=40, keep_first=2, kv_from=0, mlp=moe(40, 8, 2)),
     attention(2, 1, 32, 96, scale=0.2, diff=0.35, window=130, keep_first=65),
     latent(2, 64, 32, 64, 32, scale=0.1, base=500.0, dims=16),

@@ -227,16 +227,16 @@ def test_rotation_far_from_the_start_keeps_its_angle():
     positions = torch.arange(pos0, pos0 + T, dtype=torch.int32, device=DEV)
     seq = torch.zeros(T, dtype=torch.int32, device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    exact = torch.tensor([20000.0 ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=F64)
+    exact = torch.tensor([50000.0 ** (-2.0 * i / dims) for i in range(dims // 2)], dtype=F64)
     hi = exact.float()
     inv_freq = torch.stack([hi, (exact - hi.double()).float()]).contiguous().to(DEV)
     _, q_full = ops.latent_prepare(qp, dk, torch.ones(R, device=DEV), 1e-5, inv_freq, dims, positions, seq, table, kp, Hh, D, Dr, R, status)
     assert int(status.item()) == 0
     pos = np.arange(pos0, pos0 + T)
-    want_q = P.rotate_interleaved(qp.double().cpu().view(T, Hh, D + Dr)[:, :, D:].numpy(), 20000.0, dims, pos)
+    want_q = P.rotate_interleaved(qp.double().cpu().view(T, Hh, D + Dr)[:, :, D:].numpy(), 50000.0, dims, pos)
     got_q = q_full.double().cpu().view(T, Hh, R + Dr)[:, :, R:].numpy()
     assert np.abs(got_q - want_q).max() < 3e-6
-    want_k = P.rotate_interleaved(dk.double().cpu()[:, R:].numpy(), 20000.0, dims, pos)
+    want_k = P.rotate_interleaved(dk.double().cpu()[:, R:].numpy(), 50000.0, dims, pos)
     got_k = np.stack([kp[int(table[0, p // 64]), 0, p % 64, R:].double().cpu().numpy() for p in pos])
     assert np.abs(got_k - want_k).max() < 3e-6
 
