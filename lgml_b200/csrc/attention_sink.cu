@@ -24,7 +24,8 @@ LGML_DEFINE_LAST_ERROR(lgml_attention_sink)
 namespace {
 constexpr int ITEMS = 256;
 constexpr int WARPS = 4;
-constexpr int MAX_D = 256;
+constexpr int MAX_D = 256;        // the split decode forms (a lane holds 8 value columns)
+constexpr int GEN_MAX_D = 512;    // the general form
 
 // v_mode: 0 store v as it is; 1 also keep it in v_keep (float32 [tokens, Hkv Dv]); 2 mix with v_keep first
 template <typename T>
@@ -78,8 +79,8 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
     int window, int keep_first, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float qs[MAX_D];
-    __shared__ float acc_w[WARPS][MAX_D];
+    __shared__ float qs[GEN_MAX_D];
+    __shared__ float acc_w[WARPS][GEN_MAX_D];
     __shared__ float m_w[WARPS], l_w[WARPS];
     const int t = blockIdx.x, h = blockIdx.y;
     const int g = h / (H / Hkv);
@@ -97,9 +98,9 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
     __syncthreads();
 
     float m = -INFINITY, l = 0.f;
-    float acc[MAX_D / 32];
+    float acc[GEN_MAX_D / 32];
 #pragma unroll
-    for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
+    for (int i = 0; i < GEN_MAX_D / 32; ++i) acc[i] = 0.f;
 
     // the visible keys in order: the kept first tokens, then the window; warp w takes every WARPS-th
     for (int i = warp; i < n_keys; i += WARPS) {
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
         const float p = expf(s - m_new);
         l = l * corr + p;
 #pragma unroll
-        for (int i2 = 0; i2 < MAX_D / 32; ++i2) {
+        for (int i2 = 0; i2 < GEN_MAX_D / 32; ++i2) {
             const int d = lane + 32 * i2;
             if (d < Dv) acc[i2] = acc[i2] * corr + p * to_f32(act_load(v_pages + vcell * ldv + d));
         }
@@ -131,7 +132,7 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
         l_w[warp] = l;
     }
 #pragma unroll
-    for (int i = 0; i < MAX_D / 32; ++i) {
+    for (int i = 0; i < GEN_MAX_D / 32; ++i) {
         const int d = lane + 32 * i;
         if (d < Dv) acc_w[warp][d] = acc[i];
     }
@@ -1042,7 +1043,7 @@ LGML_API int lgml_sink_attention(const void *q, int dtype, int ldq, const int *p
     LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && Hv > 0 && D > 0 && Dv > 0 && page_size > 0 && max_blocks > 0, "sink_attention: bad sizes");
     LGML_REQUIRE(H % Hkv == 0, "sink_attention: %d heads are no multiple of %d KV heads", H, Hkv);
     LGML_REQUIRE(Hkv % Hv == 0, "sink_attention: %d key heads are no multiple of %d value heads", Hkv, Hv);
-    LGML_REQUIRE(D <= MAX_D && Dv <= MAX_D, "sink_attention: head sizes %d and %d must be at most %d", D, Dv, MAX_D);
+    LGML_REQUIRE(D <= GEN_MAX_D && Dv <= GEN_MAX_D, "sink_attention: head sizes %d and %d must be at most %d", D, Dv, GEN_MAX_D);
     LGML_REQUIRE(ldv >= Dv, "sink_attention: value rows %d apart hold no %d values", ldv, Dv);
     LGML_REQUIRE(H <= 65535, "sink_attention: too many heads");
     LGML_REQUIRE(window >= 0 && keep_first >= 0, "sink_attention: bad window");

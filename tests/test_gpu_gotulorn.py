@@ -121,13 +121,15 @@ def test_masked_attention_edges_of_the_window_and_of_the_kept_tokens(dtype, form
             assert float((other - want).abs().max()) > 5 * tol, (w2, k2)
 
 
-def test_masked_attention_float32_output_and_values_inside_the_key_cells():
-    """bfloat16 keys with a float32 result, and values that are the first Dv entries of the key cells."""
+@pytest.mark.parametrize("D,Dv", [(40, 24), (300, 288)])
+def test_masked_attention_float32_output_and_values_inside_the_key_cells(D, Dv):
+    """bfloat16 keys with a float32 result, and values that are the first Dv entries of the key cells; also at
+    cell sizes beyond what the split and tensor-core forms take."""
     from lgml_b200 import ops
 
     torch.manual_seed(3)
-    T, Hq, D, Dv = 150, 3, 40, 24
-    q = (torch.randn(T, Hq, D, dtype=F64) * 0.4).to(torch.bfloat16).double()
+    T, Hq = 150, 3
+    q = (torch.randn(T, Hq, D, dtype=F64) * 0.4 * (40 / D) ** 0.5).to(torch.bfloat16).double()
     k = (torch.randn(T, 1, D, dtype=F64)).to(torch.bfloat16).double()
     for dtype in (torch.float32, torch.bfloat16):
         kp, _, table = paged(T, 1, D, 1, 1, dtype)
