@@ -216,7 +216,8 @@ LGML_API int lgml_moe_router(const void *h, int dtype, int ldh, const float *wr,
     LGML_REQUIRE(X <= 8192, "moe_router: at most 8192 experts");
     if (n_tokens == 0) return 0;
     const size_t smem = sizeof(float) * ((size_t)((X + 3) & ~3) + (size_t)E);
-    LGML_REQUIRE(smem <= 48 * 1024, "moe_router: %d experts and rows of %d do not fit shared memory", X, E);
+    LGML_REQUIRE(smem <= 200 * 1024, "moe_router: %d experts and rows of %d do not fit shared memory", X, E);
+    if (need_smem(moe_router_kernel<float>, smem, "moe_router") || need_smem(moe_router_kernel<__nv_bfloat16>, smem, "moe_router")) return -1;
     if (dtype == LGML_F32)
         lgml_launch(moe_router_kernel<float>, n_tokens, 128, smem, stream, (const float *)h, ldh, wr, br, ids, wts, E, X, top);
     else if (dtype == LGML_BF16)
@@ -477,6 +478,7 @@ LGML_API int lgml_moe_experts_grouped(const void *h, int ldh, const int *ids, co
     const int need = (n_rows + G_TM - 1) / G_TM + (X < n_rows ? X : n_rows);
     LGML_REQUIRE(max_tiles >= need, "moe_experts_grouped: room for %d tiles, %d may be needed", max_tiles, need);
     int *n_tiles = tiles + 3 * max_tiles;
+    if (need_smem(moe_group_kernel, sizeof(int) * 4 * (size_t)X, "moe_experts_grouped")) return -1;
     lgml_launch(moe_group_kernel, 1, 1024, sizeof(int) * 4 * (size_t)X, stream, ids, n_rows, X, rows, tiles, n_tiles, max_tiles);
     dim3 g0(max_tiles, (F + G_TN / 2 - 1) / (G_TN / 2)), g1(max_tiles, (E + G_TN - 1) / G_TN);
     LGML_REQUIRE(g0.y <= 65535 && g1.y <= 65535, "moe_experts_grouped: too many columns");
@@ -550,6 +552,7 @@ LGML_API int lgml_moe_group_rows(const int *ids, int *rows, int *tiles, int max_
     const int need = (n_rows + G_TM - 1) / G_TM + (X < n_rows ? X : n_rows);
     LGML_REQUIRE(max_tiles >= need, "moe_group_rows: room for %d tiles, %d may be needed", max_tiles, need);
     if (n_tokens == 0) return 0;
+    if (need_smem(moe_group_kernel, sizeof(int) * 4 * (size_t)X, "moe_group_rows")) return -1;
     lgml_launch(moe_group_kernel, 1, 1024, sizeof(int) * 4 * (size_t)X, stream, ids, n_rows, X, rows, tiles, tiles + 3 * max_tiles, max_tiles);
     return lgml_launch_status("moe_group_rows");
 }
